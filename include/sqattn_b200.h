@@ -1,0 +1,194 @@
+/*
+ * sqattn_b200 -- C ABI of the B200 (sm_100a) SQAttn attention path.
+ *
+ * Every entry point takes plain pointers and sizes, enqueues its work on the
+ * given CUDA stream and returns a status code; nothing here allocates device
+ * memory, synchronises the device or aborts.  All tensor pointers are device
+ * pointers unless a comment says "host".  Strides are in ELEMENTS and the
+ * last (head_dim) dimension must be contiguous.  Paths in the comments are
+ * files of the reference project (yifu-ding/LongContext_SQAttn_paddle) whose
+ * interface the entry point replaces.
+ */
+#ifndef SQATTN_B200_H_
+#define SQATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* sqattn_stream_t; /* a cudaStream_t */
+
+/* status codes (0 = ok); sqattn_last_error_string() describes the last failure on this thread */
+enum {
+  SQATTN_OK = 0,
+  SQATTN_ERR_INVALID_ARG = 1, /* null pointer, bad shape/stride/alignment, bad enum (reference: ValueError / assert) */
+  SQATTN_ERR_UNSUPPORTED = 2, /* head_dim not 64/128, too many heads, ... */
+  SQATTN_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed */
+  SQATTN_ERR_WORKSPACE = 4,   /* workspace missing or too small */
+  SQATTN_ERR_DEVICE_TIMEOUT = 5 /* reported by sqattn_check_device_status: a bounded device-side wait gave up */
+};
+
+enum { SQATTN_F16 = 0, SQATTN_BF16 = 1 };
+
+/* logical [batch, heads, seq, head_dim] view of any layout (HND or NHD) */
+typedef struct {
+  const void* ptr;
+  int64_t stride_b, stride_h, stride_n;
+} sqattn_tensor;
+
+typedef struct {
+  void* ptr;
+  int64_t stride_b, stride_h, stride_n;
+} sqattn_tensor_out;
+
+/* ---- prefill ------------------------------------------------------------------------------ */
+
+enum {
+  SQATTN_MODE_DENSE_CAUSAL = 0,    /* attn_causal, sqattn/attn_triton.py:216-315 (BLOCK_M=128) */
+  SQATTN_MODE_RELATIVE_WINDOW = 1, /* attn_hierarchical_relative_window, sqattn/attn_triton_mix_relative.py:309-483 (BLOCK_M=64) */
+  SQATTN_MODE_ABSOLUTE_WINDOW = 2  /* attn_hierarchical_window, sqattn/attn_triton_mix_bad.py:285-426 (BLOCK_M=128) */
+};
+
+enum {
+  SQATTN_P_FP8_OFF = 0,
+  SQATTN_P_FP8_ALL = 1,   /* is_P_fp8_quant=True of the reference kernels (attn_triton.py:81-83) */
+  SQATTN_P_FP8_STAGE2 = 2 /* FP8 rounding of P only on int4-window tiles; 16-bit P elsewhere */
+};
+
+typedef struct {
+  /* q_*: [B, Hq, qo_len, D]; k_*, v: [B, Hkv, kv_len, D]; o: [B, Hq, qo_len, D].
+   * q_int4/k_int4 may alias q_int8/k_int8 (what the relative launcher ships, mix_relative.py:440-446).
+   * Dense mode reads only q_int8/k_int8/v. */
+  sqattn_tensor q_int8, k_int8, q_int4, k_int4, v;
+  sqattn_tensor_out o;
+  float* lse; /* optional [B, Hq, qo_len] fp32, base-2: log2(l)+m (attn_triton.py:210-213) */
+  int32_t batch, num_q_heads, num_kv_heads, qo_len, kv_len, head_dim; /* head_dim 64 or 128 */
+  int32_t qk_dtype, v_dtype, o_dtype; /* SQATTN_F16 / SQATTN_BF16 */
+  int32_t mode;
+  int32_t sink_size;            /* windows modes; relative mode needs a multiple of 64 */
+  const float* win8_ratios;     /* host, [Hq]: relative mode (fractions of kv_len) */
+  const float* win4_ratios;     /* host, [Hq] */
+  const int32_t* win8_sizes;    /* host, [Hq]: absolute mode (tokens) */
+  const int32_t* win4_sizes;    /* host, [Hq] */
+  int32_t p_fp8_mode;
+  int32_t q_is_scaled; /* 0: q is multiplied by 1/sqrt(D)*1.44269504 in its dtype first (what the reference
+                          launchers do, mix_relative.py:383-385) into the workspace; 1: caller already did */
+  void* workspace;     /* device scratch, sqattn_prefill_workspace_bytes() bytes, 1024-byte aligned */
+  size_t workspace_bytes;
+} sqattn_prefill_args;
+
+/* Replaces the launch halves of attn_causal / attn_hierarchical_relative_window /
+ * attn_hierarchical_window (files above).  Scratch is needed when q has to be scaled
+ * (q_is_scaled == 0) and when v is bf16 (the P*V product runs in fp16 like the reference's
+ * v.to(fp16), attn_triton.py:84, so a bf16 v is converted once). */
+size_t sqattn_prefill_workspace_bytes(const sqattn_prefill_args* args);
+int sqattn_prefill(const sqattn_prefill_args* args, sqattn_stream_t stream);
+
+/* ---- adapter input preparation ------------------------------------------------------------ */
+
+enum { SQATTN_QTYPE_INT = 0, SQATTN_QTYPE_E4M3 = 1, SQATTN_QTYPE_E5M2 = 2 };
+
+typedef struct {
+  /* inputs as the model hands them over: q [B, N, Hq, D], k/v [B, N, Hkv, D] viewed through strides */
+  sqattn_tensor q, k, v;
+  /* outputs, contiguous [B, H, N, D] (K/V keep Hkv heads: the reference's repeat_kv copies are
+   * bit-identical, so they are not materialised).  q outputs are already multiplied by
+   * 1/sqrt(D)*1.44269504 in the input dtype.  v_bit8 is written as fp16. */
+  void *q_bit8, *q_bit4, *k_bit8, *k_bit4, *v_bit8;
+  int32_t batch, num_q_heads, num_kv_heads, seq_len, head_dim;
+  int32_t dtype;             /* input dtype; q/k outputs use it too */
+  int32_t qk_qtype, v_qtype; /* SQATTN_QTYPE_* (args.qk_qtype / args.v_qtype of the reference) */
+  int32_t round_half_even;   /* 0: ties away from zero (paddle.round); 1: ties to even */
+  int32_t skip_bit4;         /* 1: q_bit4/k_bit4 are not needed (not written) */
+  void* workspace;           /* device scratch, sqattn_prep_workspace_bytes() bytes (K column sums) */
+  size_t workspace_bytes;
+} sqattn_prep_args;
+
+/* Replaces attention_fn's input preparation, sqattn/attn_replacer.py:334-365:
+ * K minus its sequence mean, INT8/INT4 per-token fake-quant of Q and K, INT8
+ * per-(token,channel) fake-quant of V (sqattn/fake_quant.py:23-125, 151-248). */
+size_t sqattn_prep_workspace_bytes(const sqattn_prep_args* args);
+int sqattn_prep_qkv(const sqattn_prep_args* args, sqattn_stream_t stream);
+
+/* ---- decode ------------------------------------------------------------------------------- */
+
+typedef struct {
+  sqattn_tensor q;         /* [B, Hq, 1, D] */
+  sqattn_tensor k, v;      /* [B, Hkv, kv_capacity, D] */
+  sqattn_tensor_out o;     /* [B, Hq, 1, D] */
+  float* lse;              /* optional [B, Hq] fp32 base-2 */
+  int32_t batch, num_q_heads, num_kv_heads, head_dim;
+  int32_t kv_len;          /* used for every sequence when kv_lens == NULL */
+  const int32_t* kv_lens;  /* host, [B] or NULL: ragged batch */
+  int32_t dtype, o_dtype;
+  int32_t p_fp8;           /* is_P_fp8_quant */
+  int32_t q_is_scaled;     /* 0: the kernel applies 1/sqrt(D)*1.44269504 in q's dtype on load */
+  int32_t num_splits;      /* 0 = let the length-aware scheduler choose */
+  void* workspace;         /* device scratch, sqattn_decode_workspace_bytes() bytes */
+  size_t workspace_bytes;
+  /* multi-GPU split-KV: when partial_o != NULL the merge is skipped and the per-sequence partial
+   * (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of THIS call's keys is written there for sqattn_decode_merge */
+  float* partial_o;
+  float* partial_lse;
+} sqattn_decode_args;
+
+/* Replaces attn_unified's decode branch + _attn_decode_fwd, sqattn/attn_triton_decode.py:175-241,
+ * 244-361, as a split-KV kernel.  K is NOT re-centred here (the reference does it per call, 268-269):
+ * softmax of one query is invariant to a constant shift of K, so callers centre once or not at all. */
+size_t sqattn_decode_workspace_bytes(const sqattn_decode_args* args);
+int sqattn_decode(const sqattn_decode_args* args, sqattn_stream_t stream);
+
+/* Merge num_parts partial results laid out [num_parts, rows, D] / [num_parts, rows] (e.g. the
+ * all-gathered per-GPU partials): O = sum 2^(lse_i-max) O_i / sum 2^(lse_i-max).  rows = B*Hq. */
+int sqattn_decode_merge(const float* partial_o, const float* partial_lse, int32_t num_parts, int64_t rows,
+                        int32_t head_dim, void* o, int32_t o_dtype, float* lse, sqattn_stream_t stream);
+
+/* ---- kmeans (cache_hub/kmeans.py) --------------------------------------------------------- */
+
+/* _triton_assign_kernel, kmeans.py:7-79: idx[g,t] = argmax_c <data[g,t], centroids[g,c]> (lowest c on
+ * ties, exact: near-ties of the fp32 scores are re-evaluated in fp64); sums[g,c,:] (fp64, exact) and
+ * counts[g,c] accumulate the members.  sums/counts must be zeroed by the caller.
+ * data [G,T,D], centroids [G,K,D] contiguous, dtype f16/bf16, D in {64,128}, K % 32 == 0. */
+int sqattn_kmeans_assign(const void* data, const void* centroids, int32_t dtype, int32_t groups,
+                         int32_t num_tokens, int32_t num_centroids, int32_t head_dim, int32_t* idx,
+                         double* sums, int32_t* counts, sqattn_stream_t stream);
+/* _triton_update_kernel, kmeans.py:82-124: centroid = sums/counts where counts > 0, optional L2 normalise. */
+int sqattn_kmeans_update(void* centroids, int32_t dtype, const double* sums, const int32_t* counts,
+                         int32_t groups, int32_t num_centroids, int32_t head_dim, int32_t normalize,
+                         sqattn_stream_t stream);
+/* triton_reverse_index, kmeans.py:199-262: member lists sorted by token index.
+ * cluster_size [G,K] (output), clusters [G,K,max_cluster_size] (zero-filled by the caller). */
+int sqattn_kmeans_reverse_index(const int32_t* idx, int32_t groups, int32_t num_tokens, int32_t num_centroids,
+                                int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size,
+                                sqattn_stream_t stream);
+/* triton_index_add, kmeans.py:265-329: value sums per cluster; out [G,K,D] in the value dtype.
+ * sums_ws: zeroed fp64 scratch [G,K,D]. */
+int sqattn_kmeans_index_add(const void* value, int32_t dtype, const int32_t* idx, int32_t groups,
+                            int32_t num_tokens, int32_t num_centroids, int32_t head_dim, double* sums_ws,
+                            void* out, sqattn_stream_t stream);
+/* max over counts[G*K] into *out_max (device int32, zeroed by the caller): data_cnt.max(), kmeans.py:195 */
+int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, sqattn_stream_t stream);
+
+/* ---- KV cache block mover (cache_hub/flash_attn_cache.py:7-19, 143-151, 200-227) ---------- */
+
+/* Gather rows [row0, row0+rows) of a [*, row_elems] 16-bit matrix that lives in (pinned) host or device
+ * memory into dst with one cudaMemcpy2DAsync on the given (side) stream. */
+int sqattn_cache_copy_rows(void* dst, int64_t dst_row_stride_bytes, const void* src, int64_t src_row_stride_bytes,
+                           int64_t row_bytes, int64_t rows, int32_t to_device, sqattn_stream_t stream);
+
+/* ---- diagnostics -------------------------------------------------------------------------- */
+
+/* Device-side waits (TMA / tensor-core completion barriers) are bounded; a wait that gives up records a
+ * code in a device word that this call reads back (it synchronises the stream).  Returns SQATTN_OK or
+ * SQATTN_ERR_DEVICE_TIMEOUT. */
+int sqattn_check_device_status(sqattn_stream_t stream);
+const char* sqattn_last_error_string(void);
+int sqattn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SQATTN_B200_H_ */

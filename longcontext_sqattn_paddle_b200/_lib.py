@@ -1,0 +1,116 @@
+"""ctypes binding of libsqattn_b200.so (the C ABI declared in include/sqattn_b200.h).
+
+The library is the product: there is no fallback.  Importing this module when
+the shared object has not been built raises at once.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsqattn_b200.so")
+
+F16, BF16 = 0, 1
+MODE_DENSE_CAUSAL, MODE_RELATIVE_WINDOW, MODE_ABSOLUTE_WINDOW = 0, 1, 2
+P_FP8_OFF, P_FP8_ALL, P_FP8_STAGE2 = 0, 1, 2
+QTYPE = {"int": 0, "e4m3": 1, "e5m2": 2}
+
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = range(6)
+
+
+class SqattnError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"sqattn_b200 error {code}: {msg}")
+        self.code = code
+
+
+class Tensor(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_n", C.c_int64)]
+
+
+class PrefillArgs(C.Structure):
+    _fields_ = [
+        ("q_int8", Tensor), ("k_int8", Tensor), ("q_int4", Tensor), ("k_int4", Tensor), ("v", Tensor), ("o", Tensor),
+        ("lse", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("qo_len", C.c_int32),
+        ("kv_len", C.c_int32), ("head_dim", C.c_int32),
+        ("qk_dtype", C.c_int32), ("v_dtype", C.c_int32), ("o_dtype", C.c_int32),
+        ("mode", C.c_int32), ("sink_size", C.c_int32),
+        ("win8_ratios", C.POINTER(C.c_float)), ("win4_ratios", C.POINTER(C.c_float)),
+        ("win8_sizes", C.POINTER(C.c_int32)), ("win4_sizes", C.POINTER(C.c_int32)),
+        ("p_fp8_mode", C.c_int32), ("q_is_scaled", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class PrepArgs(C.Structure):
+    _fields_ = [
+        ("q", Tensor), ("k", Tensor), ("v", Tensor),
+        ("q_bit8", C.c_void_p), ("q_bit4", C.c_void_p), ("k_bit8", C.c_void_p), ("k_bit4", C.c_void_p),
+        ("v_bit8", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("seq_len", C.c_int32),
+        ("head_dim", C.c_int32), ("dtype", C.c_int32), ("qk_qtype", C.c_int32), ("v_qtype", C.c_int32),
+        ("round_half_even", C.c_int32), ("skip_bit4", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", Tensor), ("k", Tensor), ("v", Tensor), ("o", Tensor), ("lse", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("kv_len", C.c_int32), ("kv_lens", C.POINTER(C.c_int32)),
+        ("dtype", C.c_int32), ("o_dtype", C.c_int32), ("p_fp8", C.c_int32), ("q_is_scaled", C.c_int32),
+        ("num_splits", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p),
+    ]
+
+
+# every symbol include/sqattn_b200.h declares: (name, restype, argtypes)
+SYMBOLS = [
+    ("sqattn_prefill_workspace_bytes", C.c_size_t, [C.POINTER(PrefillArgs)]),
+    ("sqattn_prefill", C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
+    ("sqattn_prep_workspace_bytes", C.c_size_t, [C.POINTER(PrepArgs)]),
+    ("sqattn_prep_qkv", C.c_int, [C.POINTER(PrepArgs), C.c_void_p]),
+    ("sqattn_decode_workspace_bytes", C.c_size_t, [C.POINTER(DecodeArgs)]),
+    ("sqattn_decode", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    ("sqattn_decode_merge", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32,
+                                      C.c_void_p, C.c_void_p]),
+    ("sqattn_kmeans_assign", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    ("sqattn_kmeans_update", C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_int32, C.c_void_p]),
+    ("sqattn_kmeans_reverse_index", C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                              C.c_void_p, C.c_void_p]),
+    ("sqattn_kmeans_index_add", C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_void_p, C.c_void_p, C.c_void_p]),
+    ("sqattn_kmeans_max_count", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    ("sqattn_cache_copy_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
+                                         C.c_void_p]),
+    ("sqattn_check_device_status", C.c_int, [C.c_void_p]),
+    ("sqattn_last_error_string", C.c_char_p, []),
+    ("sqattn_version", C.c_int, []),
+]
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()' or "
+        "python -m longcontext_sqattn_paddle_b200.build). There is no CPU or PyTorch fallback.")
+
+lib = C.CDLL(LIB_PATH)
+for _name, _res, _args in SYMBOLS:
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(code: int):
+    """Raise for a non-zero status, mapping argument errors to ValueError like the reference does."""
+    if code == OK:
+        return
+    msg = lib.sqattn_last_error_string().decode()
+    if code in (ERR_INVALID_ARG, ERR_UNSUPPORTED):
+        raise ValueError(msg)
+    raise SqattnError(code, msg)

@@ -1,0 +1,343 @@
+// Split-KV single-query (decode) attention.  HBM-bound: the job is to stream K and V exactly once at
+// full bandwidth.  One CTA handles one (sequence, KV head, key range) work item for ALL query heads of
+// the KV group, so the group's K/V are read once (the reference reads them once per query head,
+// sqattn/attn_triton_decode.py:204-241).
+//   warp 4      TMA producer: 64-key K and V tiles into a 3-stage shared-memory ring (128-byte swizzle)
+//   warps 0..3  16 keys of every tile each: S = q K^T and O += P V on mma.sync m16n8k16 (query heads padded
+//               to the 16-row M dimension), warp-shuffle row max / sum, private online-softmax state;
+//               the four states are merged through shared memory at the end of the item.
+// A second kernel merges the per-range partials (base-2 LSE).
+#pragma once
+#include <cuda.h>
+
+#include "prep.cuh"
+#include "ptx.cuh"
+
+namespace sq {
+
+constexpr int kDecMaxBatch = 128;
+constexpr int kDecTile = 64;
+constexpr int kDecStages = 3;
+
+struct DecodeParams {
+  const uint8_t* q;
+  long long q_sb, q_sh;
+  float* part_o;    // [items, Hq, D] fp32, each normalised by its own l
+  float* part_lse;  // [items, Hq]
+  int batch, hq, hkv, groups, d;
+  int chunk;  // keys per work item (multiple of 64)
+  int p_fp8, q_is_scaled;
+  float sm_scale;  // 1/sqrt(D) * 1.44269504 evaluated in double on the host, like the Python launcher
+  int lens[kDecMaxBatch];
+  int item_prefix[kDecMaxBatch + 1];  // first work item of each sequence
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <bool BF16>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (BF16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+template <int D>
+struct DecodeSmem {
+  static constexpr int kTileBytes = kDecTile * D * 2;            // one K or V tile
+  static constexpr int kStageBytes = 2 * kTileBytes;             // K then V
+  static constexpr int kBarOff = kDecStages * kStageBytes;       // full[3], empty[3]
+  static constexpr int kMiscOff = kBarOff + 8 * 2 * kDecStages;  // abort flag
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynBytes = kTotal + 1024;
+  // the merge scratch (4 warps x (16 x D fp32 + 32 floats)) reuses the tile ring
+  static_assert(4 * (16 * D + 32) * 4 <= kDecStages * kStageBytes, "merge scratch must fit in the ring");
+};
+
+// byte offset of 16-byte chunk `chunk` of key row `key` inside a [64 keys][D] tile stored as D/64 halves of
+// 128-byte rows with the TMA 128-byte swizzle
+__device__ __forceinline__ uint32_t tile_off(int key, int chunk) {
+  return static_cast<uint32_t>((chunk >> 3) * (kDecTile * 128) + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(160, 2)
+decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const __grid_constant__ DecodeParams p) {
+  using L = DecodeSmem<D>;
+  if (*reinterpret_cast<volatile int*>(&g_device_status) != 0) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar_full = sbase + L::kBarOff, bar_empty = bar_full + 8 * kDecStages;
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item -> (sequence, key range): binary search in the per-sequence item prefix
+  const int item = blockIdx.x, kvh = blockIdx.y;
+  int lo = 0, hi = p.batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.item_prefix[mid] <= item) lo = mid; else hi = mid;
+  }
+  const int bi = lo;
+  const int len = p.lens[bi];
+  const int key_begin = (item - p.item_prefix[bi]) * p.chunk;
+  const int key_end = min(len, key_begin + p.chunk);
+  const int ntiles = (key_end - key_begin + kDecTile - 1) / kDecTile;
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    for (int i = 0; i < kDecStages; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 4); }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+      bool ok = true;
+      for (int t = 0; ok && t < ntiles; ++t) {
+        const int st = t % kDecStages;
+        ok = mbar_wait(bar_empty + 8 * st, ((t / kDecStages) & 1) ^ 1, cta_abort, 201);
+        if (!ok) break;
+        mbar_expect_tx(bar_full + 8 * st, L::kStageBytes);
+        const int key0 = key_begin + t * kDecTile;
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_4d(sbase + st * L::kStageBytes + h * (kDecTile * 128), &tm_k, bar_full + 8 * st, h * 64, key0, kvh, bi);
+          tma_load_4d(sbase + st * L::kStageBytes + L::kTileBytes + h * (kDecTile * 128), &tm_v, bar_full + 8 * st, h * 64,
+                      key0, kvh, bi);
+        }
+      }
+    }
+  } else {
+    // ---- q fragments: rows = query heads of this KV group (padded to 16), 16 head_dim values per k-step
+    const int g = lane >> 2, tq = lane & 3;
+    const float sm_scale = p.sm_scale;
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int row = g + (r & 1) * 8;
+        const int col = kk * 16 + tq * 2 + (r >> 1) * 8;
+        uint32_t v = 0;
+        if (row < p.groups) {
+          const uint8_t* src = p.q + 2 * (bi * p.q_sb + static_cast<long long>(kvh * p.groups + row) * p.q_sh + col);
+          v = *reinterpret_cast<const uint32_t*>(src);
+          if (!p.q_is_scaled) {
+            const float a = to_f32<BF16>(static_cast<uint16_t>(v & 0xffffu)) * sm_scale;
+            const float b = to_f32<BF16>(static_cast<uint16_t>(v >> 16)) * sm_scale;
+            v = static_cast<uint32_t>(from_f32<BF16>(a)) | (static_cast<uint32_t>(from_f32<BF16>(b)) << 16);
+          }
+        }
+        qa[kk][r] = v;
+      }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_r[2] = {-INFINITY, -INFINITY};
+    float l_r[2] = {0.f, 0.f};  // per-lane partial row sums; reduced across the 4 lanes of a row at the end
+    const int wk = warp * 16;   // this warp's keys inside a tile
+    bool ok = true;
+    for (int t = 0; ok && t < ntiles; ++t) {
+      const int st = t % kDecStages;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * st, (t / kDecStages) & 1, cta_abort, 202));
+      if (!ok) break;
+      const uint32_t k_tile = sbase + st * L::kStageBytes, v_tile = k_tile + L::kTileBytes;
+      const int key0 = key_begin + t * kDecTile + wk;  // first key of this warp
+      if (key0 < key_end) {
+        // rows past the end of the sequence may hold anything (the cache is larger than the sequence):
+        // their scores are masked below, and their V rows are zeroed so that 0 * garbage cannot make a NaN
+        if (key0 + 16 > key_end) {
+          for (int r = key_end - key0; r < 16; ++r)
+            for (int c = lane; c < D / 8; c += 32)
+              *reinterpret_cast<uint4*>(smem + st * L::kStageBytes + L::kTileBytes + tile_off(wk + r, c)) =
+                  make_uint4(0, 0, 0, 0);
+          __syncwarp();
+        }
+        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          uint32_t b0, b1, b2, b3;
+          // matrices: (keys 0-7, d lo) (keys 0-7, d hi) (keys 8-15, d lo) (keys 8-15, d hi)
+          const int mi = lane >> 3, r = lane & 7;
+          ldmatrix_x4(k_tile + tile_off(wk + r + (mi >> 1) * 8, kk * 2 + (mi & 1)), b0, b1, b2, b3);
+          mma_16816<BF16>(s[0], qa[kk], b0, b1);
+          mma_16816<BF16>(s[1], qa[kk], b2, b3);
+        }
+        // mask keys past the end; row maxima over this warp's 16 keys
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = key0 + nb * 8 + tq * 2 + (e & 1);
+            if (key >= key_end) s[nb][e] = -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+          }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+          const float m_new = fmaxf(m_r[r], mx[r]);
+          const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+          alpha[r] = ex2_approx(m_r[r] - m_use);
+          m_r[r] = m_new;
+          mx[r] = m_use;
+        }
+        uint32_t pa[4];
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          float pv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { pv[e] = ex2_approx(s[nb][e] - mx[e >> 1]); sum[e >> 1] += pv[e]; }
+          uint32_t lo16, hi16;
+          if (p.p_fp8) {
+            lo16 = p_fp8_round_f16x2(pv[0], pv[1]);
+            hi16 = p_fp8_round_f16x2(pv[2], pv[3]);
+            if (BF16) {  // V is bf16: the f16 result is re-rounded to bf16 for the tensor-core product
+              const __half2 a = *reinterpret_cast<__half2*>(&lo16), b = *reinterpret_cast<__half2*>(&hi16);
+              lo16 = pack_bf16x2(__low2float(a), __high2float(a));
+              hi16 = pack_bf16x2(__low2float(b), __high2float(b));
+            }
+          } else {
+            lo16 = BF16 ? pack_bf16x2(pv[0], pv[1]) : pack_f16x2(pv[0], pv[1]);
+            hi16 = BF16 ? pack_bf16x2(pv[2], pv[3]) : pack_f16x2(pv[2], pv[3]);
+          }
+          pa[nb * 2] = lo16;      // rows g,   keys nb*8 + ...
+          pa[nb * 2 + 1] = hi16;  // rows g+8
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) l_r[r] = l_r[r] * alpha[r] + sum[r];
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+          o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int j = 0; j < D / 16; ++j) {
+          uint32_t b0, b1, b2, b3;
+          // transposed 8x8 loads: (keys 0-7, d chunk 2j) (keys 8-15, 2j) (keys 0-7, 2j+1) (keys 8-15, 2j+1)
+          const int mi = lane >> 3, r = lane & 7;
+          ldmatrix_x4_trans(v_tile + tile_off(wk + r + (mi & 1) * 8, j * 2 + (mi >> 1)), b0, b1, b2, b3);
+          mma_16816<BF16>(o[2 * j], pa, b0, b1);
+          mma_16816<BF16>(o[2 * j + 1], pa, b2, b3);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+    }
+    // ---- merge the four warps' states through shared memory (the ring is idle now)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
+      l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // all consumer warps are done with the ring
+    float* scratch = reinterpret_cast<float*>(smem);
+    float* my = scratch + warp * (16 * D + 32);
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      const int col = j * 8 + tq * 2;
+      my[g * D + col] = o[j][0]; my[g * D + col + 1] = o[j][1];
+      my[(g + 8) * D + col] = o[j][2]; my[(g + 8) * D + col + 1] = o[j][3];
+    }
+    if (tq == 0) {
+      my[16 * D + g] = m_r[0]; my[16 * D + g + 8] = m_r[1];
+      my[16 * D + 16 + g] = l_r[0]; my[16 * D + 16 + g + 8] = l_r[1];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (ok) {
+      for (int idx = threadIdx.x; idx < p.groups * D; idx += 128) {
+        const int row = idx / D, col = idx % D;
+        float mw[4], mmax = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { mw[w] = scratch[w * (16 * D + 32) + 16 * D + row]; mmax = fmaxf(mmax, mw[w]); }
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float sc = (mw[w] == -INFINITY) ? 0.f : ex2_approx(mw[w] - mmax);
+          acc += sc * scratch[w * (16 * D + 32) + row * D + col];
+          l += sc * scratch[w * (16 * D + 32) + 16 * D + 16 + row];
+        }
+        const long long orow = static_cast<long long>(item) * p.hq + kvh * p.groups + row;
+        p.part_o[orow * D + col] = (l > 0.f) ? acc / l : 0.f;
+        if (col == 0) p.part_lse[orow] = (l > 0.f) ? log2f(l) + mmax : -INFINITY;
+      }
+    }
+  }
+  if (*cta_abort) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+}
+
+struct MergeParams {
+  const float* part_o;    // [parts..., rows, D]
+  const float* part_lse;  // [parts..., rows]
+  void* o;                // rows x D in o_dtype, or fp32 when o_f32
+  float* lse;             // optional [rows]
+  long long o_sb, o_sh;   // output strides (elements) for row = b*hq + h; ignored when contiguous
+  int hq, d, o_dtype, o_f32, contiguous;
+  int num_parts;          // uniform mode: parts are [num_parts, rows, D]
+  long long rows;
+  int ragged;             // ragged mode: parts of sequence b are items item_prefix[b] .. item_prefix[b+1]-1
+  int item_prefix[kDecMaxBatch + 1];
+};
+
+// O = sum_i 2^(lse_i - max) O_i / sum_i 2^(lse_i - max);  lse = log2(sum) + max
+__global__ void decode_merge_kernel(const __grid_constant__ MergeParams p) {
+  const long long row = blockIdx.x;  // b*hq + h
+  const int b = static_cast<int>(row / p.hq), h = static_cast<int>(row % p.hq);
+  int first = 0, count = p.num_parts;
+  long long part_stride = p.rows;  // in rows
+  long long base_row = row;
+  if (p.ragged) {
+    first = p.item_prefix[b];
+    count = p.item_prefix[b + 1] - first;
+    part_stride = p.hq;
+    base_row = static_cast<long long>(first) * p.hq + h;
+  }
+  float mmax = -INFINITY;
+  for (int i = 0; i < count; ++i) mmax = fmaxf(mmax, p.part_lse[base_row + i * part_stride]);
+  for (int col = threadIdx.x; col < p.d; col += blockDim.x) {
+    float acc = 0.f, den = 0.f;
+    for (int i = 0; i < count; ++i) {
+      const float lse_i = p.part_lse[base_row + i * part_stride];
+      const float w = (lse_i == -INFINITY) ? 0.f : exp2f(lse_i - mmax);
+      den += w;
+      acc += w * p.part_o[(base_row + i * part_stride) * p.d + col];
+    }
+    const float val = (den > 0.f) ? acc / den : 0.f;
+    const long long off = p.contiguous ? row * p.d + col : b * p.o_sb + h * p.o_sh + col;
+    if (p.o_f32) reinterpret_cast<float*>(p.o)[off] = val;
+    else if (p.o_dtype) reinterpret_cast<uint16_t*>(p.o)[off] = from_f32<true>(val);
+    else reinterpret_cast<uint16_t*>(p.o)[off] = from_f32<false>(val);
+    if (col == 0 && p.lse) p.lse[row] = (den > 0.f) ? log2f(den) + mmax : -INFINITY;
+  }
+}
+
+}  // namespace sq

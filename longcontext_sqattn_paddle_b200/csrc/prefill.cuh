@@ -1,0 +1,426 @@
+// Causal GQA prefill attention for sm_100a: dense causal and the sink + hierarchical-window variants.
+//
+// One CTA owns 128 query rows of one head.  Warp roles:
+//   warp 0      TMA producer: Q tile once (again when the operand set changes), K / V tiles per 64-key step
+//   warp 1      tcgen05 issuer: S = Q K^T (smem x smem -> TMEM), O += P V (TMEM x smem -> TMEM); owns TMEM
+//   warps 2..5  online softmax, one query row per thread (TMEM lane), P written back over S in TMEM as f16
+// The step order, the 64-key max/sum update and the f16 (optionally e4m3-rounded) P are those of the
+// reference tile loop (sqattn/attn_triton_mix_relative.py:76-98 == sqattn/attn_triton.py:64-86).
+#pragma once
+#include <cuda.h>
+
+#include "ptx.cuh"
+
+namespace sq {
+
+constexpr int kMaxHeads = 128;
+constexpr int kBlockM = 128;  // query rows per CTA (tcgen05 M)
+constexpr int kBlockN = 64;   // keys per step (the reference BLOCK_N)
+constexpr int kMaxSegs = 12;
+
+// segment flags
+constexpr int kSegAct0 = 1;   // rows 0..63 of the CTA take part
+constexpr int kSegAct1 = 2;   // rows 64..127 take part
+constexpr int kSegDiag = 4;   // additive causal mask (stage 4)
+constexpr int kSegInt4 = 8;   // reads the int4 operand set (stage 2)
+constexpr int kSegFp8 = 16;   // P rounded through e4m3
+
+struct Seg {
+  int start;   // first key of the first tile
+  int ntiles;  // number of 64-key tiles
+  int flags;
+};
+
+struct PrefillParams {
+  void* o;
+  long long o_sb, o_sh, o_sn;
+  float* lse;
+  float* dump;  // debug builds only: S tiles of CTA 0
+  int batch, hq, hkv, groups, n, kv_len;
+  int mode, sink, p_fp8_mode, o_dtype, qk_bf16, same_opset, nblk;
+  int w8[kMaxHeads];
+  int w4[kMaxHeads];
+};
+
+// Key ranges of the four stages for the query block [qs, qe)
+// (attn_triton_mix_relative.py:36-75, attn_triton_mix_bad.py:41-74).
+__device__ __forceinline__ void stage_range(int stage, int qs, int qe, int w8, int w4, int sink, int& lo, int& hi) {
+  const int l4 = max(sink, qe - w4);
+  const int l8 = max(sink, qe - w8);
+  lo = hi = 0;
+  if (stage == 1) {
+    hi = min(sink, qs);
+  } else if (stage == 2) {
+    if (l4 < l8) { lo = l4; hi = l8; }
+  } else if (stage == 3) {
+    if (l8 < qs) { lo = l8; hi = qs; }
+  } else {
+    lo = qs; hi = qe;
+  }
+}
+
+// Builds the CTA's step list.  BLOCK_M = 128 modes (dense, absolute windows) have one schedule for all
+// 128 rows.  The relative-window mode has BLOCK_M = 64: the CTA covers two reference blocks whose stage
+// ranges are offset by 0 or 64 keys; their tiles are merged stage by stage and each step records which
+// half takes part, so every half sees exactly its own tiles in the reference order.
+__device__ int build_schedule(Seg* segs, const PrefillParams& p, int blk, int head) {
+  int n = 0;
+  const int stage_flags_fp8_all = (p.p_fp8_mode == 1) ? kSegFp8 : 0;
+  auto flags_of = [&](int stage) {
+    int f = stage_flags_fp8_all;
+    if (stage == 4) f |= kSegDiag;
+    if (stage == 2) {
+      if (!p.same_opset) f |= kSegInt4;
+      if (p.p_fp8_mode == 2) f |= kSegFp8;
+    }
+    return f;
+  };
+  if (p.mode == 0) {
+    const int qs = blk * kBlockM;
+    if (qs > 0) segs[n++] = Seg{0, qs / kBlockN, kSegAct0 | kSegAct1 | stage_flags_fp8_all};
+    segs[n++] = Seg{qs, kBlockM / kBlockN, kSegAct0 | kSegAct1 | kSegDiag | stage_flags_fp8_all};
+    return n;
+  }
+  const int w8 = p.w8[head], w4 = p.w4[head];
+  if (p.mode == 2) {
+    const int qs = blk * kBlockM, qe = qs + kBlockM;
+    for (int stage = 1; stage <= 4; ++stage) {
+      int lo, hi;
+      stage_range(stage, qs, qe, w8, w4, p.sink, lo, hi);
+      if (hi > lo) segs[n++] = Seg{lo, (hi - lo + kBlockN - 1) / kBlockN, kSegAct0 | kSegAct1 | flags_of(stage)};
+    }
+    return n;
+  }
+  // relative windows: two 64-row blocks
+  const int qs0 = blk * kBlockM, qs1 = qs0 + 64;
+  const bool has1 = qs1 < p.n;
+  for (int stage = 1; stage <= 4; ++stage) {
+    int lo0, hi0, lo1 = 0, hi1 = 0;
+    stage_range(stage, qs0, qs0 + 64, w8, w4, p.sink, lo0, hi0);
+    if (has1) stage_range(stage, qs1, qs1 + 64, w8, w4, p.sink, lo1, hi1);
+    const bool e0 = hi0 <= lo0, e1 = hi1 <= lo1;
+    if (e0 && e1) continue;
+    const int lo = e0 ? lo1 : (e1 ? lo0 : min(lo0, lo1));
+    const int hi = e0 ? hi1 : (e1 ? hi0 : max(hi0, hi1));
+    int run_start = 0, run_act = -1, run_len = 0;
+    for (int t = lo; t < hi; t += kBlockN) {
+      const int act = ((!e0 && t >= lo0 && t < hi0) ? kSegAct0 : 0) | ((!e1 && t >= lo1 && t < hi1) ? kSegAct1 : 0);
+      if (act != run_act) {
+        if (run_len > 0 && run_act != 0 && n < kMaxSegs) segs[n++] = Seg{run_start, run_len, run_act | flags_of(stage)};
+        run_start = t; run_act = act; run_len = 0;
+      }
+      ++run_len;
+    }
+    if (run_len > 0 && run_act != 0 && n < kMaxSegs) segs[n++] = Seg{run_start, run_len, run_act | flags_of(stage)};
+  }
+  return n;
+}
+
+template <int D>
+struct PrefillSmem {
+  static constexpr int kKStages = 2;
+  static constexpr int kVStages = 2;
+  static constexpr int kQBytes = kBlockM * D * 2;
+  static constexpr int kKBytes = kBlockN * D * 2;
+  static constexpr int kVBytes = kBlockN * D * 2;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQBytes;
+  static constexpr int kVOff = kKOff + kKStages * kKBytes;
+  static constexpr int kBarOff = kVOff + kVStages * kVBytes;
+  // barriers: q_full, q_empty, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], o_done
+  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 1;
+  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
+  static constexpr int kSegOff = kMiscOff + 16;  // tmem base, abort flag, nseg
+  static constexpr int kTotal = kSegOff + kMaxSegs * 12;
+  static constexpr int kDynBytes = kTotal + 1024;  // slack for 1024-byte alignment of the tiles
+};
+
+// Walks the flattened step list.
+struct StepIter {
+  const Seg* segs;
+  int nseg, seg, t;
+  __device__ StepIter(const Seg* s, int n) : segs(s), nseg(n), seg(0), t(0) {}
+  __device__ bool done() const { return seg >= nseg; }
+  __device__ int flags() const { return segs[seg].flags; }
+  __device__ int key0() const { return segs[seg].start + t * kBlockN; }
+  __device__ bool first_of_seg() const { return t == 0; }
+  __device__ bool last_of_seg() const { return t == segs[seg].ntiles - 1; }
+  // operand set of the next segment differs from this one's
+  __device__ bool opset_changes_after() const {
+    return seg + 1 < nseg && ((segs[seg + 1].flags ^ segs[seg].flags) & kSegInt4);
+  }
+  __device__ bool opset_changed_before() const {
+    return seg > 0 && ((segs[seg - 1].flags ^ segs[seg].flags) & kSegInt4);
+  }
+  __device__ void next() {
+    if (++t >= segs[seg].ntiles) { t = 0; ++seg; }
+  }
+};
+
+template <int D, bool kDump>
+__global__ void __launch_bounds__(192, 2)
+prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
+               const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PrefillParams p) {
+  using L = PrefillSmem<D>;
+  constexpr int KS = L::kKStages, VS = L::kVStages;
+  constexpr uint32_t kTmemCols = 256;  // S0 [0,64) S1 [64,128) O [128,128+D)
+  constexpr uint32_t kOCol = 128;
+
+  // once a wait has given up anywhere, the remaining CTAs of the grid leave at once
+  if (*reinterpret_cast<volatile int*>(&g_device_status) != 0) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t q_s = sbase + L::kQOff, k_s = sbase + L::kKOff, v_s = sbase + L::kVOff;
+  const uint32_t bars = sbase + L::kBarOff;
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
+  const uint32_t bar_k_full = bars + 16, bar_k_empty = bar_k_full + 8 * KS;
+  const uint32_t bar_v_full = bar_k_empty + 8 * KS, bar_v_empty = bar_v_full + 8 * VS;
+  const uint32_t bar_s_full = bar_v_empty + 8 * VS, bar_p_full = bar_s_full + 16, bar_o_done = bar_p_full + 16;
+  volatile uint32_t* tmem_base_s = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  volatile int* nseg_s = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 8);
+  Seg* segs = reinterpret_cast<Seg*>(smem + L::kSegOff);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Heads vary fastest so that the heads of one KV group run together and share K/V tiles in L2;
+  // later (for dense causal: longer) query blocks are launched first.
+  const int per_blk = p.hq * p.batch;
+  const int blk = p.nblk - 1 - static_cast<int>(blockIdx.x) / per_blk;
+  const int rem = static_cast<int>(blockIdx.x) % per_blk;
+  const int bi = rem / p.hq, head = rem % p.hq, kvh = head / p.groups;
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    *nseg_s = build_schedule(segs, p, blk, head);
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
+    for (int i = 0; i < KS; ++i) { mbar_init(bar_k_full + 8 * i, 1); mbar_init(bar_k_empty + 8 * i, 1); }
+    for (int i = 0; i < VS; ++i) { mbar_init(bar_v_full + 8 * i, 1); mbar_init(bar_v_empty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_s_full + 8 * i, 1); mbar_init(bar_p_full + 8 * i, 128); }
+    mbar_init(bar_o_done, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_s)), kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_base_s;
+  const int nseg = *nseg_s;
+  int nsteps = 0;
+  for (int i = 0; i < nseg; ++i) nsteps += segs[i].ntiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_v);
+      int q_loads = 0;
+      int i = 0;
+      bool ok = true;
+      for (StepIter it(segs, nseg); ok && !it.done(); it.next(), ++i) {
+        const bool int4 = it.flags() & kSegInt4;
+        if (i == 0 || (it.first_of_seg() && it.opset_changed_before())) {
+          if (q_loads > 0) ok = mbar_wait(bar_q_empty, (q_loads - 1) & 1, cta_abort, 101);
+          if (!ok) break;
+          mbar_expect_tx(bar_q_full, L::kQBytes);
+          const CUtensorMap* tq = int4 ? &tm_q4 : &tm_q8;
+#pragma unroll
+          for (int h = 0; h < D / 64; ++h) tma_load_4d(q_s + h * (kBlockM * 128), tq, bar_q_full, h * 64, blk * kBlockM, head, bi);
+          ++q_loads;
+        }
+        const int ks = i % KS, vs = i % VS;
+        ok = mbar_wait(bar_k_empty + 8 * ks, ((i / KS) & 1) ^ 1, cta_abort, 102);
+        if (!ok) break;
+        mbar_expect_tx(bar_k_full + 8 * ks, L::kKBytes);
+        const CUtensorMap* tk = int4 ? &tm_k4 : &tm_k8;
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h)
+          tma_load_4d(k_s + ks * L::kKBytes + h * (kBlockN * 128), tk, bar_k_full + 8 * ks, h * 64, it.key0(), kvh, bi);
+        ok = mbar_wait(bar_v_empty + 8 * vs, ((i / VS) & 1) ^ 1, cta_abort, 103);
+        if (!ok) break;
+        mbar_expect_tx(bar_v_full + 8 * vs, L::kVBytes);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h)
+          tma_load_4d(v_s + vs * L::kVBytes + h * (kBlockN * 128), &tm_v, bar_v_full + 8 * vs, h * 64, it.key0(), kvh, bi);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ tcgen05 issuer
+    if (lane == 0) {
+      const uint32_t fmt = p.qk_bf16 ? 1u : 0u;
+      const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, kBlockM, kBlockN);
+      const uint32_t idesc_pv = make_idesc(0, 0, 0, 1, kBlockM, D);
+      bool ok = true;
+      int q_uses = 0;
+      StepIter qk_it(segs, nseg), pv_it(segs, nseg);
+      auto issue_qk = [&](int j) {
+        if (j == 0 || (qk_it.first_of_seg() && qk_it.opset_changed_before())) {
+          ok = mbar_wait(bar_q_full, q_uses & 1, cta_abort, 111);
+          ++q_uses;
+          if (!ok) return;
+        }
+        const int ks = j % KS;
+        ok = mbar_wait(bar_k_full + 8 * ks, (j / KS) & 1, cta_abort, 112);
+        if (!ok) return;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + (j & 1) * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off_q = (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32;
+          const uint32_t off_k = (kk >> 2) * (kBlockN * 128) + (kk & 3) * 32;
+          mma_ss(d_tmem, smem_desc_sw128(q_s + off_q, 16, 1024), smem_desc_sw128(k_s + ks * L::kKBytes + off_k, 16, 1024),
+                 idesc_qk, kk > 0);
+        }
+        tc_commit(bar_s_full + 8 * (j & 1));
+        tc_commit(bar_k_empty + 8 * ks);
+        if (qk_it.last_of_seg() && qk_it.opset_changes_after()) tc_commit(bar_q_empty);
+        qk_it.next();
+      };
+      if (nsteps > 0) issue_qk(0);
+      for (int i = 0; ok && i < nsteps; ++i, pv_it.next()) {
+        if (i + 1 < nsteps) { issue_qk(i + 1); if (!ok) break; }
+        ok = mbar_wait(bar_p_full + 8 * (i & 1), (i >> 1) & 1, cta_abort, 113);
+        if (!ok) break;
+        const int vs = i % VS;
+        ok = mbar_wait(bar_v_full + 8 * vs, (i / VS) & 1, cta_abort, 114);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t p_tmem = tmem + (i & 1) * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          // V tile: [64 keys][64 d] 128-byte rows per d-half; MN-major B operand: 64-d chunks 8 KB apart
+          // (leading offset), 8-key groups 1 KB apart (stride offset); 16 keys per MMA = 2 KB.
+          mma_ts(tmem + kOCol, p_tmem + kk * 8, smem_desc_sw128(v_s + vs * L::kVBytes + kk * 2048, kBlockN * 128, 1024),
+                 idesc_pv, (i > 0 || kk > 0));
+        }
+        tc_commit(bar_v_empty + 8 * vs);
+        tc_commit(bar_o_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int quarter = warp & 3;  // TMEM lanes a warp may touch: 32*(warp%4) .. +31
+    const int row_in_tile = quarter * 32 + lane;
+    const int half_bit = (row_in_tile >= 64) ? kSegAct1 : kSegAct0;
+    const int row = blk * kBlockM + row_in_tile;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    float m_i = -INFINITY, l_i = 1.0f;
+    bool ok = true;
+    int i = 0;
+    for (StepIter it(segs, nseg); ok && !it.done(); it.next(), ++i) {
+      const int flags = it.flags();
+      const uint32_t s_tmem = tmem + lane_addr + (i & 1) * kBlockN;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + 8 * (i & 1), (i >> 1) & 1, cta_abort, 121));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pk[32];
+      float alpha = 1.0f;
+      if (flags & half_bit) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(s_tmem, r0);
+        tmem_ld32(s_tmem + 32, r1);
+        tmem_wait_ld();
+        float x[64];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) { x[c] = __uint_as_float(r0[c]); x[32 + c] = __uint_as_float(r1[c]); }
+        if (kDump && blockIdx.x == 0 && p.dump) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) p.dump[(static_cast<size_t>(i) * kBlockM + row_in_tile) * 64 + c] = x[c];
+        }
+        if (flags & kSegDiag) {
+          const int key0 = it.key0();
+#pragma unroll
+          for (int c = 0; c < 64; ++c) x[c] = x[c] + ((row >= key0 + c) ? 0.0f : -1000000.0f);
+        }
+        float mx = x[0];
+#pragma unroll
+        for (int c = 1; c < 64; ++c) mx = fmaxf(mx, x[c]);
+        const float m_new = fmaxf(m_i, mx);
+        alpha = ex2_approx(m_i - m_new);
+        float sum = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) { x[c] = ex2_approx(x[c] - m_new); sum += x[c]; }
+        l_i = l_i * alpha + sum;
+        m_i = m_new;
+        if (flags & kSegFp8) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) pk[c] = p_fp8_round_f16x2(x[2 * c], x[2 * c + 1]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) pk[c] = pack_f16x2(x[2 * c], x[2 * c + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pk[c] = 0u;
+      }
+      tmem_st32(s_tmem, pk);
+      // acc *= alpha: O lives in TMEM and is rescaled only when some row of this warp moved its maximum
+      // (alpha == 1 exactly otherwise, so skipping is bit-identical).
+      if (__any_sync(0xffffffffu, alpha != 1.0f) && i > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_o_done, (i - 1) & 1, cta_abort, 122));
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld32(tmem + lane_addr + kOCol + c0, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+          tmem_st32(tmem + lane_addr + kOCol + c0, o);
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_full + 8 * (i & 1));
+    }
+    if (ok && nsteps > 0) ok = mbar_wait(bar_o_done, (nsteps - 1) & 1, cta_abort, 123);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && nsteps > 0) {
+      tc_fence_after();
+      const bool in_range = row < p.n;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      2 * (static_cast<long long>(bi) * p.o_sb + static_cast<long long>(head) * p.o_sh +
+                           static_cast<long long>(row) * p.o_sn);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_addr + kOCol + c0, o);
+        tmem_wait_ld();
+        if (in_range) {
+          uint32_t w[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float a = __uint_as_float(o[2 * c]) / l_i, b = __uint_as_float(o[2 * c + 1]) / l_i;
+            w[c] = p.o_dtype ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) dst[c] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+        }
+      }
+      if (p.lse && in_range)
+        p.lse[(static_cast<long long>(bi) * p.hq + head) * p.n + row] = log2f(l_i) + m_i;
+    }
+    tc_fence_before();
+  }
+
+  // ------------------------------------------------------------------ tear-down (also reached after a wait gave up)
+  if (*cta_abort) {
+    // copies may still be in flight towards this CTA's shared memory: give them time to land
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace sq

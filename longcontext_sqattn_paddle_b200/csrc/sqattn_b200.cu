@@ -1,0 +1,505 @@
+// C ABI of the library (declared in include/sqattn_b200.h).  Host-side argument checking, TMA descriptor
+// construction, the length-aware decode scheduler and the kernel launches.  One translation unit.
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "decode.cuh"
+#include "kmeans.cuh"
+#include "prefill.cuh"
+#include "prep.cuh"
+
+using namespace sq;
+
+namespace {
+
+double sm_scale_log2(int head_dim) { return 1.0 / sqrt(static_cast<double>(head_dim)) * 1.44269504; }
+
+int elementwise_grid(long long work_items, int block) {
+  long long g = (work_items + block - 1) / block;
+  const long long cap = 148ll * 16;  // a few waves of the 148 SMs; kernels use grid-stride loops
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+View4 view_of(const sqattn_tensor& t, int b, int h, int n, int d) {
+  View4 v;
+  v.ptr = static_cast<const uint8_t*>(t.ptr);
+  v.sb = t.stride_b; v.sh = t.stride_h; v.sn = t.stride_n;
+  v.b = b; v.h = h; v.n = n; v.d = d;
+  return v;
+}
+
+bool aligned16(const sqattn_tensor& t) {
+  return (reinterpret_cast<uintptr_t>(t.ptr) % 16 == 0) && (t.stride_b % 8 == 0) && (t.stride_h % 8 == 0) &&
+         (t.stride_n % 8 == 0);
+}
+
+// relative window size: ((int64)(ratio_f32 * kv_len) + 127) / 128 * 128 (attn_triton_mix_relative.py:43-46)
+int relative_window(float ratio, int kv_len) {
+  const float prod = ratio * static_cast<float>(kv_len);
+  long long raw = static_cast<long long>(prod);
+  long long w = (raw + 127) / 128 * 128;
+  if (w > 0x3fffffff) w = 0x3fffffff;
+  if (w < -0x3fffffff) w = -0x3fffffff;
+  return static_cast<int>(w);
+}
+
+struct PrefillPlan {
+  size_t q8_off, q4_off, v_off, total;
+  bool scale_q, scale_q4, convert_v;
+};
+
+int plan_prefill(const sqattn_prefill_args* a, PrefillPlan* pl) {
+  if (!a) return fail(SQATTN_ERR_INVALID_ARG, "args is null");
+  if (a->head_dim != 64 && a->head_dim != 128)
+    return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128 (pad like the reference does)", a->head_dim);
+  if (a->batch <= 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->qo_len <= 0 || a->kv_len <= 0)
+    return fail(SQATTN_ERR_INVALID_ARG, "batch/heads/lengths must be positive");
+  if (a->num_q_heads % a->num_kv_heads) return fail(SQATTN_ERR_INVALID_ARG, "num_q_heads must be a multiple of num_kv_heads");
+  if (a->num_q_heads > kMaxHeads) return fail(SQATTN_ERR_UNSUPPORTED, "more than %d query heads", kMaxHeads);
+  if (a->qo_len != a->kv_len) return fail(SQATTN_ERR_INVALID_ARG, "qo_len and kv_len must be equal for causal attention");
+  const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
+  const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
+  const size_t qbytes = static_cast<size_t>(a->batch) * a->num_q_heads * a->qo_len * a->head_dim * 2;
+  const size_t vbytes = static_cast<size_t>(a->batch) * a->num_kv_heads * a->kv_len * a->head_dim * 2;
+  pl->scale_q = !a->q_is_scaled;
+  pl->scale_q4 = pl->scale_q && !alias;
+  pl->convert_v = a->v_dtype == SQATTN_BF16;
+  size_t off = 0;
+  pl->q8_off = off; if (pl->scale_q) off += align_up(qbytes, 1024);
+  pl->q4_off = off; if (pl->scale_q4) off += align_up(qbytes, 1024);
+  pl->v_off = off; if (pl->convert_v) off += align_up(vbytes, 1024);
+  pl->total = off;
+  return SQATTN_OK;
+}
+
+template <int D>
+int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStream_t stream, float* dump) {
+  const int B = a->batch, Hq = a->num_q_heads, Hkv = a->num_kv_heads, N = a->qo_len;
+  const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
+  const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const float scale = static_cast<float>(sm_scale_log2(D));
+  const bool bf16 = a->qk_dtype == SQATTN_BF16;
+
+  sqattn_tensor q8 = a->q_int8, q4 = alias ? a->q_int8 : a->q_int4, v = a->v;
+  const int64_t cont_q[3] = {static_cast<int64_t>(Hq) * N * D, static_cast<int64_t>(N) * D, D};
+  const int64_t cont_v[3] = {static_cast<int64_t>(Hkv) * a->kv_len * D, static_cast<int64_t>(a->kv_len) * D, D};
+  if (pl.scale_q) {
+    View4 in = view_of(a->q_int8, B, Hq, N, D);
+    const int grid = elementwise_grid(static_cast<long long>(B) * Hq * N * (D / 8), 256);
+    if (bf16) strided_map_kernel<true, 0><<<grid, 256, 0, stream>>>(in, ws + pl.q8_off, scale);
+    else strided_map_kernel<false, 0><<<grid, 256, 0, stream>>>(in, ws + pl.q8_off, scale);
+    q8 = sqattn_tensor{ws + pl.q8_off, cont_q[0], cont_q[1], cont_q[2]};
+    if (pl.scale_q4) {
+      View4 in4 = view_of(a->q_int4, B, Hq, N, D);
+      if (bf16) strided_map_kernel<true, 0><<<grid, 256, 0, stream>>>(in4, ws + pl.q4_off, scale);
+      else strided_map_kernel<false, 0><<<grid, 256, 0, stream>>>(in4, ws + pl.q4_off, scale);
+      q4 = sqattn_tensor{ws + pl.q4_off, cont_q[0], cont_q[1], cont_q[2]};
+    } else {
+      q4 = q8;
+    }
+  }
+  if (pl.convert_v) {
+    View4 in = view_of(a->v, B, Hkv, a->kv_len, D);
+    const int grid = elementwise_grid(static_cast<long long>(B) * Hkv * a->kv_len * (D / 8), 256);
+    strided_map_kernel<true, 1><<<grid, 256, 0, stream>>>(in, ws + pl.v_off, 1.0f);
+    v = sqattn_tensor{ws + pl.v_off, cont_v[0], cont_v[1], cont_v[2]};
+  }
+  SQ_CUDA(cudaGetLastError());
+
+  CUtensorMap tq8, tq4, tk8, tk4, tv;
+  int rc;
+  if ((rc = make_tmap_bhnd(&tq8, q8.ptr, a->qk_dtype, q8.stride_b, q8.stride_h, q8.stride_n, B, Hq, N, D, kBlockM, "q_int8"))) return rc;
+  if ((rc = make_tmap_bhnd(&tq4, q4.ptr, a->qk_dtype, q4.stride_b, q4.stride_h, q4.stride_n, B, Hq, N, D, kBlockM, "q_int4"))) return rc;
+  if ((rc = make_tmap_bhnd(&tk8, a->k_int8.ptr, a->qk_dtype, a->k_int8.stride_b, a->k_int8.stride_h, a->k_int8.stride_n, B, Hkv, a->kv_len, D, kBlockN, "k_int8"))) return rc;
+  const sqattn_tensor& k4 = alias ? a->k_int8 : a->k_int4;
+  if ((rc = make_tmap_bhnd(&tk4, k4.ptr, a->qk_dtype, k4.stride_b, k4.stride_h, k4.stride_n, B, Hkv, a->kv_len, D, kBlockN, "k_int4"))) return rc;
+  if ((rc = make_tmap_bhnd(&tv, v.ptr, SQATTN_F16, v.stride_b, v.stride_h, v.stride_n, B, Hkv, a->kv_len, D, kBlockN, "v"))) return rc;
+
+  PrefillParams p;
+  memset(&p, 0, sizeof(p));
+  p.o = a->o.ptr; p.o_sb = a->o.stride_b; p.o_sh = a->o.stride_h; p.o_sn = a->o.stride_n;
+  p.lse = a->lse; p.dump = dump;
+  p.batch = B; p.hq = Hq; p.hkv = Hkv; p.groups = Hq / Hkv; p.n = N; p.kv_len = a->kv_len;
+  p.mode = a->mode; p.sink = a->sink_size; p.p_fp8_mode = a->p_fp8_mode; p.o_dtype = a->o_dtype;
+  p.qk_bf16 = bf16; p.same_opset = alias; p.nblk = (N + kBlockM - 1) / kBlockM;
+  for (int h = 0; h < Hq; ++h) {
+    if (a->mode == SQATTN_MODE_RELATIVE_WINDOW) {
+      p.w8[h] = relative_window(a->win8_ratios[h], a->kv_len);
+      p.w4[h] = relative_window(a->win4_ratios[h], a->kv_len);
+    } else if (a->mode == SQATTN_MODE_ABSOLUTE_WINDOW) {
+      p.w8[h] = a->win8_sizes[h];
+      p.w4[h] = a->win4_sizes[h];
+    }
+  }
+  using L = PrefillSmem<D>;
+  const long long grid = static_cast<long long>(p.nblk) * Hq * B;
+  if (grid > 0x7fffffffll) return fail(SQATTN_ERR_UNSUPPORTED, "grid too large");
+  if (dump) {
+    SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
+    prefill_kernel<D, true><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);
+  } else {
+    static bool attr_set = false;
+    if (!attr_set) {
+      SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
+      attr_set = true;
+    }
+    prefill_kernel<D, false><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);
+  }
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump) {
+  PrefillPlan pl;
+  int rc = plan_prefill(a, &pl);
+  if (rc) return rc;
+  if (!a->q_int8.ptr || !a->k_int8.ptr || !a->v.ptr || !a->o.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
+  if (a->mode < 0 || a->mode > 2) return fail(SQATTN_ERR_INVALID_ARG, "unknown mode %d", a->mode);
+  if (a->p_fp8_mode < 0 || a->p_fp8_mode > 2) return fail(SQATTN_ERR_INVALID_ARG, "unknown p_fp8_mode %d", a->p_fp8_mode);
+  if (a->mode != SQATTN_MODE_DENSE_CAUSAL) {
+    if (a->sink_size < 0) return fail(SQATTN_ERR_INVALID_ARG, "sink_size must be a non-negative integer, got %d", a->sink_size);
+    if (!a->q_int4.ptr || !a->k_int4.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null int4 operand pointer");
+    if (a->mode == SQATTN_MODE_RELATIVE_WINDOW) {
+      if (a->sink_size % 64) return fail(SQATTN_ERR_INVALID_ARG, "relative windows need sink_size %% 64 == 0 (64-key tiles), got %d", a->sink_size);
+      if (!a->win8_ratios || !a->win4_ratios) return fail(SQATTN_ERR_INVALID_ARG, "window ratios missing");
+    } else if (!a->win8_sizes || !a->win4_sizes) {
+      return fail(SQATTN_ERR_INVALID_ARG, "window sizes missing");
+    }
+  }
+  if (!aligned16(a->q_int8) || !aligned16(a->k_int8) || !aligned16(a->v))
+    return fail(SQATTN_ERR_INVALID_ARG, "q/k/v need 16-byte aligned pointers and strides that are multiples of 8 elements");
+  if ((reinterpret_cast<uintptr_t>(a->o.ptr) % 16) || (a->o.stride_n % 8) || (a->o.stride_h % 8) || (a->o.stride_b % 8))
+    return fail(SQATTN_ERR_INVALID_ARG, "o needs a 16-byte aligned pointer and strides that are multiples of 8 elements");
+  if (pl.total > 0 && (!a->workspace || a->workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(a->workspace) % 1024)))
+    return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (1024-byte aligned) required", pl.total);
+  return a->head_dim == 128 ? launch_prefill<128>(a, pl, stream, dump) : launch_prefill<64>(a, pl, stream, dump);
+}
+
+// ---- decode scheduling ---------------------------------------------------------------------------------
+struct DecodePlan {
+  int chunk;
+  int total_items;
+  int prefix[kDecMaxBatch + 1];
+  int lens[kDecMaxBatch];
+};
+
+// Length-aware scheduler: every work item covers `chunk` keys of one sequence; chunk is chosen so that all
+// sequences together give about two waves of CTAs (2 CTAs per SM), never less than 256 keys per item.
+int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
+  if (!a) return fail(SQATTN_ERR_INVALID_ARG, "args is null");
+  if (a->head_dim != 64 && a->head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", a->head_dim);
+  if (a->batch <= 0 || a->batch > kDecMaxBatch) return fail(SQATTN_ERR_UNSUPPORTED, "batch must be in [1, %d]", kDecMaxBatch);
+  if (a->num_kv_heads <= 0 || a->num_q_heads % a->num_kv_heads) return fail(SQATTN_ERR_INVALID_ARG, "bad head counts");
+  if (a->num_q_heads / a->num_kv_heads > 16) return fail(SQATTN_ERR_UNSUPPORTED, "more than 16 query heads per KV head");
+  long long total_tiles = 0;
+  for (int b = 0; b < a->batch; ++b) {
+    const int len = a->kv_lens ? a->kv_lens[b] : a->kv_len;
+    if (len <= 0) return fail(SQATTN_ERR_INVALID_ARG, "kv length of sequence %d is %d", b, len);
+    pl->lens[b] = len;
+    total_tiles += (len + kDecTile - 1) / kDecTile;
+  }
+  int chunk;
+  if (a->num_splits > 0) {
+    int maxlen = 0;
+    for (int b = 0; b < a->batch; ++b) maxlen = pl->lens[b] > maxlen ? pl->lens[b] : maxlen;
+    chunk = (maxlen + a->num_splits - 1) / a->num_splits;
+  } else {
+    const long long target = 148ll * 2 * 2 / a->num_kv_heads + 1;  // items per KV head
+    chunk = static_cast<int>((total_tiles + target - 1) / target) * kDecTile;
+  }
+  chunk = (chunk + kDecTile - 1) / kDecTile * kDecTile;
+  if (chunk < 256) chunk = 256;
+  pl->chunk = chunk;
+  int items = 0;
+  for (int b = 0; b < a->batch; ++b) {
+    pl->prefix[b] = items;
+    items += (pl->lens[b] + chunk - 1) / chunk;
+  }
+  pl->prefix[a->batch] = items;
+  pl->total_items = items;
+  return SQATTN_OK;
+}
+
+size_t decode_ws_bytes(const sqattn_decode_args* a, const DecodePlan& pl) {
+  const size_t rows = static_cast<size_t>(pl.total_items) * a->num_q_heads;
+  return align_up(rows * a->head_dim * 4, 256) + align_up(rows * 4, 256);
+}
+
+template <int D, bool BF16>
+int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_t stream) {
+  CUtensorMap tk, tv;
+  int rc;
+  // the maps cover the whole cache capacity of each sequence; lengths are enforced in the kernel
+  int cap = 0;
+  for (int b = 0; b < a->batch; ++b) cap = pl.lens[b] > cap ? pl.lens[b] : cap;
+  if ((rc = make_tmap_bhnd(&tk, a->k.ptr, a->dtype, a->k.stride_b, a->k.stride_h, a->k.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "k"))) return rc;
+  if ((rc = make_tmap_bhnd(&tv, a->v.ptr, a->dtype, a->v.stride_b, a->v.stride_h, a->v.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "v"))) return rc;
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const uint8_t*>(a->q.ptr); p.q_sb = a->q.stride_b; p.q_sh = a->q.stride_h;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const size_t rows = static_cast<size_t>(pl.total_items) * a->num_q_heads;
+  p.part_o = reinterpret_cast<float*>(ws);
+  p.part_lse = reinterpret_cast<float*>(ws + align_up(rows * D * 4, 256));
+  p.batch = a->batch; p.hq = a->num_q_heads; p.hkv = a->num_kv_heads; p.groups = a->num_q_heads / a->num_kv_heads; p.d = D;
+  p.chunk = pl.chunk; p.p_fp8 = a->p_fp8; p.q_is_scaled = a->q_is_scaled;
+  p.sm_scale = static_cast<float>(sm_scale_log2(D));
+  memcpy(p.lens, pl.lens, sizeof(int) * a->batch);
+  memcpy(p.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
+  using L = DecodeSmem<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    SQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
+    attr_set = true;
+  }
+  dim3 grid(pl.total_items, a->num_kv_heads);
+  decode_kernel<D, BF16><<<grid, 160, L::kDynBytes, stream>>>(tk, tv, p);
+  SQ_CUDA(cudaGetLastError());
+
+  MergeParams m;
+  memset(&m, 0, sizeof(m));
+  m.part_o = p.part_o; m.part_lse = p.part_lse;
+  m.hq = a->num_q_heads; m.d = D; m.ragged = 1; m.rows = static_cast<long long>(a->batch) * a->num_q_heads;
+  memcpy(m.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
+  if (a->partial_o) {
+    m.o = a->partial_o; m.lse = a->partial_lse; m.o_f32 = 1; m.contiguous = 1;
+  } else {
+    m.o = a->o.ptr; m.lse = a->lse; m.o_dtype = a->o_dtype; m.o_sb = a->o.stride_b; m.o_sh = a->o.stride_h;
+  }
+  decode_merge_kernel<<<static_cast<unsigned>(m.rows), D, 0, stream>>>(m);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t sqattn_prefill_workspace_bytes(const sqattn_prefill_args* args) {
+  PrefillPlan pl;
+  if (plan_prefill(args, &pl)) return 0;
+  return pl.total;
+}
+
+int sqattn_prefill(const sqattn_prefill_args* args, sqattn_stream_t stream) {
+  return prefill_impl(args, reinterpret_cast<cudaStream_t>(stream), nullptr);
+}
+
+#ifdef SQATTN_DEBUG_EXPORTS
+// Debug builds only: same as sqattn_prefill, and CTA 0 additionally writes every S tile it sees
+// ([steps][128 rows][64 keys] fp32) to `dump`.
+int sqattn_debug_prefill_dump(const sqattn_prefill_args* args, float* dump, sqattn_stream_t stream) {
+  return prefill_impl(args, reinterpret_cast<cudaStream_t>(stream), dump);
+}
+#endif
+
+size_t sqattn_prep_workspace_bytes(const sqattn_prep_args* a) {
+  if (!a) return 0;
+  return static_cast<size_t>(a->batch) * a->num_kv_heads * (kMeanChunks + 1) * a->head_dim * sizeof(float);
+}
+
+int sqattn_prep_qkv(const sqattn_prep_args* a, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!a) return fail(SQATTN_ERR_INVALID_ARG, "args is null");
+  if (a->head_dim != 64 && a->head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", a->head_dim);
+  if (a->qk_qtype < 0 || a->qk_qtype > 2) return fail(SQATTN_ERR_INVALID_ARG, "Invalid quantization type: %d", a->qk_qtype);
+  if (a->v_qtype < 0 || a->v_qtype > 2) return fail(SQATTN_ERR_INVALID_ARG, "Invalid quantization type: %d", a->v_qtype);
+  if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->q_bit8 || !a->k_bit8 || !a->v_bit8) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
+  if (!a->skip_bit4 && (!a->q_bit4 || !a->k_bit4)) return fail(SQATTN_ERR_INVALID_ARG, "q_bit4/k_bit4 missing");
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v)) return fail(SQATTN_ERR_INVALID_ARG, "inputs need 16-byte alignment");
+  if (a->batch <= 0 || a->seq_len <= 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  const size_t need = sqattn_prep_workspace_bytes(a);
+  if (!a->workspace || a->workspace_bytes < need) return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes required", need);
+  const int B = a->batch, N = a->seq_len, D = a->head_dim, Hq = a->num_q_heads, Hkv = a->num_kv_heads;
+  const bool bf16 = a->dtype == SQATTN_BF16;
+  float* partial = static_cast<float*>(a->workspace);
+  float* mean = partial + static_cast<size_t>(B) * Hkv * kMeanChunks * D;
+  View4 kq = view_of(a->q, B, Hq, N, D), kk = view_of(a->k, B, Hkv, N, D), kv = view_of(a->v, B, Hkv, N, D);
+  const int lanes = 256 / (D / 8);
+  dim3 mg(kMeanChunks, B * Hkv);
+  if (bf16) kmean_partial_kernel<true><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
+  else kmean_partial_kernel<false><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
+  kmean_final_kernel<<<B * Hkv, 128, 0, stream>>>(partial, mean, D, N);
+  const float qs = static_cast<float>(sm_scale_log2(D));
+  uint8_t* q4 = a->skip_bit4 ? nullptr : static_cast<uint8_t*>(a->q_bit4);
+  uint8_t* k4 = a->skip_bit4 ? nullptr : static_cast<uint8_t*>(a->k_bit4);
+  const int rows_per_block = 256 / (D / 8);
+  const int gq = elementwise_grid((static_cast<long long>(B) * Hq * N + rows_per_block - 1) / rows_per_block, 1);
+  const int gk = elementwise_grid((static_cast<long long>(B) * Hkv * N + rows_per_block - 1) / rows_per_block, 1);
+  const int gv = elementwise_grid(static_cast<long long>(N) * (D / 8), 256);
+  if (bf16) {
+    quant_rows_kernel<true, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, a->qk_qtype, a->round_half_even, qs);
+    quant_rows_kernel<true, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, a->qk_qtype, a->round_half_even, 1.0f);
+    quant_v_kernel<true><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), a->v_qtype, a->round_half_even);
+  } else {
+    quant_rows_kernel<false, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, a->qk_qtype, a->round_half_even, qs);
+    quant_rows_kernel<false, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, a->qk_qtype, a->round_half_even, 1.0f);
+    quant_v_kernel<false><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), a->v_qtype, a->round_half_even);
+  }
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+size_t sqattn_decode_workspace_bytes(const sqattn_decode_args* args) {
+  DecodePlan pl;
+  if (plan_decode(args, &pl)) return 0;
+  return decode_ws_bytes(args, pl);
+}
+
+int sqattn_decode(const sqattn_decode_args* a, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  DecodePlan pl;
+  int rc = plan_decode(a, &pl);
+  if (rc) return rc;
+  if (!a->q.ptr || !a->k.ptr || !a->v.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
+  if (!a->partial_o && !a->o.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null output pointer");
+  if (a->partial_o && !a->partial_lse) return fail(SQATTN_ERR_INVALID_ARG, "partial_lse missing");
+  if (!aligned16(a->k) || !aligned16(a->v)) return fail(SQATTN_ERR_INVALID_ARG, "k/v need 16-byte alignment");
+  if ((reinterpret_cast<uintptr_t>(a->q.ptr) % 4) || (a->q.stride_h % 2) || (a->q.stride_b % 2)) return fail(SQATTN_ERR_INVALID_ARG, "q needs 4-byte alignment");
+  const size_t need = decode_ws_bytes(a, pl);
+  if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) % 256))
+    return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required", need);
+  const bool bf16 = a->dtype == SQATTN_BF16;
+  if (a->head_dim == 128) return bf16 ? launch_decode<128, true>(a, pl, stream) : launch_decode<128, false>(a, pl, stream);
+  return bf16 ? launch_decode<64, true>(a, pl, stream) : launch_decode<64, false>(a, pl, stream);
+}
+
+int sqattn_decode_merge(const float* partial_o, const float* partial_lse, int32_t num_parts, int64_t rows,
+                        int32_t head_dim, void* o, int32_t o_dtype, float* lse, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!partial_o || !partial_lse || !o) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (num_parts <= 0 || rows <= 0 || head_dim <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  MergeParams m;
+  memset(&m, 0, sizeof(m));
+  m.part_o = partial_o; m.part_lse = partial_lse; m.o = o; m.lse = lse;
+  m.hq = 1; m.d = head_dim; m.o_dtype = o_dtype; m.contiguous = 1; m.num_parts = num_parts; m.rows = rows;
+  decode_merge_kernel<<<static_cast<unsigned>(rows), head_dim < 128 ? 64 : 128, 0, stream>>>(m);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+// ---- kmeans ------------------------------------------------------------------------------------------
+#define SQ_KM_DISPATCH(KERNEL, ...)                                         \
+  do {                                                                      \
+    if (head_dim == 128) {                                                  \
+      if (bf16) KERNEL<128, true> __VA_ARGS__; else KERNEL<128, false> __VA_ARGS__; \
+    } else {                                                                \
+      if (bf16) KERNEL<64, true> __VA_ARGS__; else KERNEL<64, false> __VA_ARGS__;   \
+    }                                                                       \
+  } while (0)
+
+static int km_check(int32_t groups, int32_t num_tokens, int32_t num_centroids, int32_t head_dim) {
+  if (head_dim != 64 && head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", head_dim);
+  if (groups <= 0 || num_tokens <= 0 || num_centroids <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  if (num_centroids % 32) return fail(SQATTN_ERR_INVALID_ARG, "num_centroids must be a multiple of 32");
+  return SQATTN_OK;
+}
+
+int sqattn_kmeans_assign(const void* data, const void* centroids, int32_t dtype, int32_t groups, int32_t num_tokens,
+                         int32_t num_centroids, int32_t head_dim, int32_t* idx, double* sums, int32_t* counts,
+                         sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int rc = km_check(groups, num_tokens, num_centroids, head_dim);
+  if (rc) return rc;
+  if (!data || !centroids || !idx) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  const bool bf16 = dtype == SQATTN_BF16;
+  const uint8_t* d8 = static_cast<const uint8_t*>(data);
+  const uint8_t* c8 = static_cast<const uint8_t*>(centroids);
+  dim3 grid((num_tokens + kKmTokens - 1) / kKmTokens, groups);
+  SQ_KM_DISPATCH(kmeans_assign_kernel, <<<grid, 256, 0, stream>>>(d8, c8, idx, num_tokens, num_centroids));
+  const long long warps = static_cast<long long>(groups) * num_tokens;
+  const unsigned rgrid = static_cast<unsigned>((warps * 32 + 255) / 256);
+  SQ_KM_DISPATCH(kmeans_recheck_kernel, <<<rgrid, 256, 0, stream>>>(d8, c8, idx, groups, num_tokens, num_centroids));
+  if (sums) {
+    const long long thr = warps * (head_dim / 8);
+    const unsigned agrid = static_cast<unsigned>((thr + 255) / 256);
+    SQ_KM_DISPATCH(kmeans_accumulate_kernel, <<<agrid, 256, 0, stream>>>(d8, idx, sums, counts, groups, num_tokens, num_centroids));
+  }
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_kmeans_update(void* centroids, int32_t dtype, const double* sums, const int32_t* counts, int32_t groups,
+                         int32_t num_centroids, int32_t head_dim, int32_t normalize, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int rc = km_check(groups, 1, num_centroids, head_dim);
+  if (rc) return rc;
+  if (!centroids || !sums || !counts) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  const bool bf16 = dtype == SQATTN_BF16;
+  const long long total = static_cast<long long>(groups) * num_centroids;
+  const unsigned grid = static_cast<unsigned>((total + 127) / 128);
+  uint8_t* c8 = static_cast<uint8_t*>(centroids);
+  SQ_KM_DISPATCH(kmeans_update_kernel, <<<grid, 128, 0, stream>>>(c8, sums, counts, total, normalize));
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_kmeans_reverse_index(const int32_t* idx, int32_t groups, int32_t num_tokens, int32_t num_centroids,
+                                int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size,
+                                sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!idx || !clusters || !cluster_size) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (groups <= 0 || num_tokens <= 0 || num_centroids <= 0 || max_cluster_size <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  kmeans_reverse_index_kernel<<<groups, 1024, 0, stream>>>(idx, num_tokens, num_centroids, max_cluster_size, clusters, cluster_size);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_kmeans_index_add(const void* value, int32_t dtype, const int32_t* idx, int32_t groups, int32_t num_tokens,
+                            int32_t num_centroids, int32_t head_dim, double* sums_ws, void* out,
+                            sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int rc = km_check(groups, num_tokens, num_centroids, head_dim);
+  if (rc) return rc;
+  if (!value || !idx || !sums_ws || !out) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  const bool bf16 = dtype == SQATTN_BF16;
+  const uint8_t* v8 = static_cast<const uint8_t*>(value);
+  const long long thr = static_cast<long long>(groups) * num_tokens * (head_dim / 8);
+  SQ_KM_DISPATCH(kmeans_accumulate_kernel, <<<static_cast<unsigned>((thr + 255) / 256), 256, 0, stream>>>(v8, idx, sums_ws, nullptr, groups, num_tokens, num_centroids));
+  const long long n = static_cast<long long>(groups) * num_centroids * head_dim;
+  if (bf16) kmeans_store_sums_kernel<true><<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(sums_ws, static_cast<uint8_t*>(out), n);
+  else kmeans_store_sums_kernel<false><<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(sums_ws, static_cast<uint8_t*>(out), n);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!counts || !out_max || n <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad arguments");
+  max_int_kernel<<<elementwise_grid(n, 256), 256, 0, stream>>>(counts, n, out_max);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+// ---- cache ---------------------------------------------------------------------------------------------
+int sqattn_cache_copy_rows(void* dst, int64_t dst_row_stride_bytes, const void* src, int64_t src_row_stride_bytes,
+                           int64_t row_bytes, int64_t rows, int32_t to_device, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!dst || !src || row_bytes <= 0 || rows <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad arguments");
+  if (dst_row_stride_bytes < row_bytes || src_row_stride_bytes < row_bytes) return fail(SQATTN_ERR_INVALID_ARG, "row stride smaller than row");
+  SQ_CUDA(cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_row_stride_bytes), src, static_cast<size_t>(src_row_stride_bytes),
+                            static_cast<size_t>(row_bytes), static_cast<size_t>(rows),
+                            to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, stream));
+  return SQATTN_OK;
+}
+
+// ---- diagnostics -----------------------------------------------------------------------------------------
+int sqattn_check_device_status(sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int code = 0;
+  SQ_CUDA(cudaMemcpyFromSymbolAsync(&code, g_device_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream));
+  SQ_CUDA(cudaStreamSynchronize(stream));
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbolAsync(g_device_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+    return fail(SQATTN_ERR_DEVICE_TIMEOUT, "a device-side wait gave up (code %d: 1xx prefill, 2xx decode)", code);
+  }
+  return SQATTN_OK;
+}
+
+const char* sqattn_last_error_string(void) { return err_buf(); }
+int sqattn_version(void) { return 100; }
+
+}  // extern "C"

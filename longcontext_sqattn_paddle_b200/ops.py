@@ -1,0 +1,181 @@
+"""Tensor-level wrappers over the C ABI: they only translate torch tensors
+(device memory, strides, the current stream) into the plain structs of
+include/sqattn_b200.h.  No arithmetic happens on the Python side."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib as L
+
+
+def _dt(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return L.F16
+    if dtype == torch.bfloat16:
+        return L.BF16
+    raise ValueError(f"unsupported dtype {dtype}: float16 or bfloat16 expected")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("sqattn_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def _view(t: torch.Tensor, layout: str) -> L.Tensor:
+    """Logical [B,H,N,D] view of a 4-D tensor stored HND or NHD."""
+    assert t.dim() == 4 and t.stride(-1) == 1, "Last dim of qkv must be contiguous."
+    if layout == "HND":
+        return L.Tensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+    if layout == "NHD":
+        return L.Tensor(t.data_ptr(), t.stride(0), t.stride(2), t.stride(1))
+    raise ValueError(f"tensor_layout {layout} not supported")
+
+
+def _shape(t: torch.Tensor, layout: str):
+    b, x, y, d = t.shape
+    return (b, x, y, d) if layout == "HND" else (b, y, x, d)
+
+
+def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
+    if nbytes == 0:
+        return None
+    ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+    off = (-ws.data_ptr()) % 1024
+    return ws[off:off + nbytes]
+
+
+def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0, layout: str = "HND",
+            out_dtype=torch.float16, return_lse: bool = False, p_fp8_mode: int = 0, q_is_scaled: bool = False,
+            out: Optional[torch.Tensor] = None, out_layout: Optional[str] = None):
+    """sqattn_prefill.  win8/win4: per-head sequences (floats for the relative mode, ints for the absolute)."""
+    _require_cuda(q8, k8, q4, k4, v)
+    b, hq, n, d = _shape(q8, layout)
+    _, hkv, kv_len, _ = _shape(k8, layout)
+    if out is None:
+        out = torch.empty(q8.shape, dtype=out_dtype, device=q8.device)
+        out_layout = layout
+    lse = torch.empty(b, hq, n, dtype=torch.float32, device=q8.device) if return_lse else None
+    a = L.PrefillArgs()
+    a.q_int8, a.k_int8 = _view(q8, layout), _view(k8, layout)
+    a.q_int4, a.k_int4 = _view(q4, layout), _view(k4, layout)
+    a.v, a.o = _view(v, layout), _view(out, out_layout)
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.batch, a.num_q_heads, a.num_kv_heads, a.qo_len, a.kv_len, a.head_dim = b, hq, hkv, n, kv_len, d
+    a.qk_dtype, a.v_dtype, a.o_dtype = _dt(q8.dtype), _dt(v.dtype), _dt(out.dtype)
+    a.mode, a.sink_size, a.p_fp8_mode, a.q_is_scaled = mode, int(sink), int(p_fp8_mode), int(q_is_scaled)
+    keep = []
+    if mode == L.MODE_RELATIVE_WINDOW:
+        r8 = (C.c_float * hq)(*[float(x) for x in win8])
+        r4 = (C.c_float * hq)(*[float(x) for x in win4])
+        a.win8_ratios, a.win4_ratios = r8, r4
+        keep += [r8, r4]
+    elif mode == L.MODE_ABSOLUTE_WINDOW:
+        s8 = (C.c_int32 * hq)(*[int(x) for x in win8])
+        s4 = (C.c_int32 * hq)(*[int(x) for x in win4])
+        a.win8_sizes, a.win4_sizes = s8, s4
+        keep += [s8, s4]
+    need = L.lib.sqattn_prefill_workspace_bytes(C.byref(a))
+    ws = _workspace(need, q8.device)
+    a.workspace, a.workspace_bytes = (ws.data_ptr() if ws is not None else None), need
+    L.check(L.lib.sqattn_prefill(C.byref(a), _stream()))
+    return (out, lse) if return_lse else out
+
+
+def prep_qkv(query, key, value, *, qk_qtype: str = "int", v_qtype: str = "int", round_half_even: bool = False,
+             skip_bit4: bool = False):
+    """sqattn_prep_qkv: NHD inputs -> (q_bit8, q_bit4, k_bit8, k_bit4, v_bit8) contiguous HND; q pre-scaled,
+    K/V with their own Hkv heads, v_bit8 in fp16."""
+    _require_cuda(query, key, value)
+    if qk_qtype not in L.QTYPE:
+        raise ValueError(f"Invalid quantization type: {qk_qtype}")
+    if v_qtype not in L.QTYPE:
+        raise ValueError(f"Invalid quantization type: {v_qtype}")
+    b, n, hq, d = query.shape
+    hkv = key.shape[2]
+    dev = query.device
+    q8 = torch.empty(b, hq, n, d, dtype=query.dtype, device=dev)
+    k8 = torch.empty(b, hkv, n, d, dtype=query.dtype, device=dev)
+    q4 = None if skip_bit4 else torch.empty_like(q8)
+    k4 = None if skip_bit4 else torch.empty_like(k8)
+    v8 = torch.empty(b, hkv, n, d, dtype=torch.float16, device=dev)
+    a = L.PrepArgs()
+    a.q, a.k, a.v = _view(query, "NHD"), _view(key, "NHD"), _view(value, "NHD")
+    a.q_bit8, a.k_bit8, a.v_bit8 = q8.data_ptr(), k8.data_ptr(), v8.data_ptr()
+    a.q_bit4 = None if q4 is None else q4.data_ptr()
+    a.k_bit4 = None if k4 is None else k4.data_ptr()
+    a.batch, a.num_q_heads, a.num_kv_heads, a.seq_len, a.head_dim = b, hq, hkv, n, d
+    a.dtype, a.qk_qtype, a.v_qtype = _dt(query.dtype), L.QTYPE[qk_qtype], L.QTYPE[v_qtype]
+    a.round_half_even, a.skip_bit4 = int(round_half_even), int(skip_bit4)
+    need = L.lib.sqattn_prep_workspace_bytes(C.byref(a))
+    ws = _workspace(need, dev)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need
+    L.check(L.lib.sqattn_prep_qkv(C.byref(a), _stream()))
+    return q8, q4, k8, k4, v8
+
+
+def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse: bool = False, p_fp8: bool = False,
+           q_is_scaled: bool = False, kv_lens: Optional[Sequence[int]] = None, kv_len: Optional[int] = None,
+           num_splits: int = 0, partial: bool = False):
+    """sqattn_decode.  q [B,Hq,1,D] (HND) or [B,1,Hq,D] (NHD); k/v caches of capacity >= kv_len.
+    partial=True returns (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of these keys for a later merge."""
+    _require_cuda(q, k, v)
+    b, hq, one, d = _shape(q, layout)
+    assert one == 1
+    _, hkv, cap, _ = _shape(k, layout)
+    a = L.DecodeArgs()
+    a.q, a.k, a.v = _view(q, layout), _view(k, layout), _view(v, layout)
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = b, hq, hkv, d
+    a.kv_len = int(cap if kv_len is None else kv_len)
+    lens = None
+    if kv_lens is not None:
+        lens = (C.c_int32 * b)(*[int(x) for x in kv_lens])
+        a.kv_lens = lens
+    a.dtype, a.p_fp8, a.q_is_scaled, a.num_splits = _dt(k.dtype), int(p_fp8), int(q_is_scaled), int(num_splits)
+    out = lse = po = pl = None
+    if partial:
+        po = torch.empty(b, hq, d, dtype=torch.float32, device=q.device)
+        pl = torch.empty(b, hq, dtype=torch.float32, device=q.device)
+        a.partial_o, a.partial_lse = po.data_ptr(), pl.data_ptr()
+        a.o_dtype = L.F16
+    else:
+        out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
+        a.o = _view(out, layout)
+        a.o_dtype = _dt(out_dtype)
+        if return_lse:
+            lse = torch.empty(b, hq, 1, dtype=torch.float32, device=q.device)
+            a.lse = lse.data_ptr()
+    need = L.lib.sqattn_decode_workspace_bytes(C.byref(a))
+    if need == 0:  # the plan was rejected: let the entry point report why
+        L.check(L.lib.sqattn_decode(C.byref(a), _stream()))
+        raise ValueError("sqattn_decode: invalid arguments")
+    ws = _workspace(need, q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need
+    L.check(L.lib.sqattn_decode(C.byref(a), _stream()))
+    if partial:
+        return po, pl
+    return (out, lse) if return_lse else out
+
+
+def decode_merge(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype=torch.float16, return_lse: bool = False):
+    """sqattn_decode_merge: part_o [P, rows, D] fp32, part_lse [P, rows] fp32 -> O [rows, D]."""
+    _require_cuda(part_o, part_lse)
+    p, rows, d = part_o.shape
+    out = torch.empty(rows, d, dtype=out_dtype, device=part_o.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=part_o.device) if return_lse else None
+    L.check(L.lib.sqattn_decode_merge(part_o.contiguous().data_ptr(), part_lse.contiguous().data_ptr(), p, rows, d,
+                                      out.data_ptr(), _dt(out_dtype), None if lse is None else lse.data_ptr(),
+                                      _stream()))
+    return (out, lse) if return_lse else out
+
+
+def check_device_status():
+    """Raise if a bounded device-side wait gave up since the last check (synchronises the stream)."""
+    L.check(L.lib.sqattn_check_device_status(_stream()))

@@ -1,0 +1,154 @@
+"""Parity of the CUDA prefill path with the CPU oracle (through the C ABI).
+
+Tolerance (stated by the task): max-abs error of O below 2e-2 against the oracle's emulation for bf16/fp16
+outputs.  Tile order, 64-key max updates and the f16 / e4m3 rounding of P are the same on both sides, so the
+observed error is the 16-bit output rounding plus fp32 accumulation-order noise; LSE (fp32) agrees to 2e-3."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sqattn_oracle as so
+
+pytestmark = pytest.mark.gpu
+TOL_O = 2e-2
+TOL_LSE = 2e-3
+
+
+@pytest.fixture(scope="module")
+def sq():
+    from longcontext_sqattn_paddle_b200 import ops, sqattn
+    yield sqattn
+    torch.cuda.synchronize()
+    ops.check_device_status()
+
+
+def _rand(shape, seed, dtype, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def _cmp(o, lse, ro, rlse, tol_o=TOL_O, rows=None):
+    o, lse = o.float().cpu(), lse.cpu()
+    if rows is not None:
+        o, ro, lse, rlse = o[:, :, rows], ro[:, :, rows], lse[:, :, rows], rlse[:, :, rows]
+    assert torch.isfinite(o).all()
+    eo = (o - ro.float()).abs().max().item()
+    el = (lse - rlse).abs().max().item()
+    assert eo < tol_o, f"max|dO|={eo}"
+    assert el < TOL_LSE, f"max|dLSE|={el}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,d,hq,hkv", [(128, 128, 1, 1), (320, 128, 4, 2), (1000, 64, 6, 2), (2048, 128, 7, 1)])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_dense_causal(sq, dtype, n, d, hq, hkv, fp8):
+    q, k, v = (_rand((1, h, n, d), s, dtype) for h, s in ((hq, 1), (hkv, 2), (hkv, 3)))
+    o, lse = sq.attn_causal(q.cuda(), k.cuda(), v.cuda(), "HND", dtype, True, fp8)
+    ro, rlse = so.dense_causal(q, k, v, output_dtype=dtype, return_lse=True, is_P_fp8_quant=fp8)
+    _cmp(o, lse, ro, rlse)
+
+
+def test_dense_causal_nhd_batch(sq):
+    dtype = torch.bfloat16
+    q, k, v = _rand((2, 512, 4, 128), 4, dtype), _rand((2, 512, 2, 128), 5, dtype), _rand((2, 512, 2, 128), 6, dtype)
+    o, lse = sq.attn_causal(q.cuda(), k.cuda(), v.cuda(), "NHD", dtype, True, False)
+    ro, rlse = so.dense_causal(q, k, v, tensor_layout="NHD", output_dtype=dtype, return_lse=True)
+    assert o.shape == q.shape
+    _cmp(o.permute(0, 2, 1, 3), lse, ro.permute(0, 2, 1, 3), rlse)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,d,sink,r8,r4", [
+    (1024, 128, 256, [0.1, 0.1, 0.1, 0.1], [0.1, 0.1, 0.1, 0.1]),   # the reference's effective default
+    (1024, 64, 64, [0.2, 0.5, 0.3, 1.0], [0.6, 0.5, 0.9, 0.0]),
+    (1500, 128, 128, [0.05, 0.3, 0.0, 0.7], [0.4, 0.3, 0.5, 0.2]),
+])
+@pytest.mark.parametrize("fp8", ["off", "all", "stage2"])
+def test_relative_windows(sq, dtype, n, d, sink, r8, r4, fp8):
+    hq, hkv = 4, 2
+    q8, k8, v = _rand((1, hq, n, d), 7, dtype), _rand((1, hkv, n, d), 8, dtype), _rand((1, hkv, n, d), 9, dtype)
+    q4 = (q8.float() + 0.05 * _rand(q8.shape, 10, torch.float32)).to(dtype)
+    k4 = (k8.float() + 0.05 * _rand(k8.shape, 11, torch.float32)).to(dtype)
+    for use4 in (False, True):
+        o, lse = sq.attn_hierarchical_relative_window(q8.cuda(), k8.cuda(), q4.cuda(), k4.cuda(), v.cuda(), r8, r4, sink,
+                                                      "HND", dtype, True, p_fp8_mode=fp8, use_int4_operands=use4)
+        ro, rlse = so.windowed_prefill(q8, k8, q4, k4, v, r8, r4, sink, mode="relative", output_dtype=dtype,
+                                       return_lse=True, p_fp8_mode=fp8, use_int4_operands=use4)
+        _cmp(o, lse, ro, rlse)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,d,sink,w8,w4", [
+    (512, 64, 64, [128, 192], [320, 256]),
+    (1100, 128, 100, [200, 77], [333, 500]),   # unaligned sink and windows: tiles start at arbitrary keys
+    (768, 128, 256, 128, 384),
+])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_absolute_windows(sq, dtype, n, d, sink, w8, w4, fp8):
+    hq, hkv = 2, 1
+    q8, k8, v = _rand((1, hq, n, d), 12, dtype), _rand((1, hkv, n, d), 13, dtype), _rand((1, hkv, n, d), 14, dtype)
+    q4 = (q8.float() + 0.05 * _rand(q8.shape, 15, torch.float32)).to(dtype)
+    k4 = (k8.float() + 0.05 * _rand(k8.shape, 16, torch.float32)).to(dtype)
+    w8t = w8 if isinstance(w8, int) else torch.tensor(w8, dtype=torch.int32)
+    w4t = w4 if isinstance(w4, int) else torch.tensor(w4, dtype=torch.int32)
+    o, lse = sq.attn_hierarchical_window(q8.cuda(), k8.cuda(), q4.cuda(), k4.cuda(), v.cuda(), w8t, w4t, sink, "HND",
+                                         dtype, True, fp8)
+    ro, rlse = so.windowed_prefill(q8, k8, q4, k4, v, w8t, w4t, sink, mode="absolute", output_dtype=dtype,
+                                   return_lse=True, is_P_fp8_quant=fp8)
+    _cmp(o, lse, ro, rlse)
+
+
+@pytest.mark.parametrize("name", ["relative", "absolute", "dense"])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_against_reference_golden(sq, golden_dir, name, fp8):
+    """The CUDA path against the vectors produced by the reference's own Triton kernels."""
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    g = {k: torch.from_numpy(z[k]) for k in z.files if z[k].shape != ()}
+    if name == "relative":
+        o, lse = sq.attn_hierarchical_relative_window(g["q"].cuda(), g["k"].cuda(), g["q"].cuda(), g["k"].cuda(),
+                                                      g["v"].cuda(), g["r8"], g["r4"], int(z["sink"]), "HND",
+                                                      torch.float16, True, fp8)
+    elif name == "absolute":
+        o, lse = sq.attn_hierarchical_window(g["q8"].cuda(), g["k8"].cuda(), g["q4"].cuda(), g["k4"].cuda(),
+                                             g["v"].cuda(), g["w8"], g["w4"], int(z["sink"]), "HND", torch.float16,
+                                             True, fp8)
+    else:
+        o, lse = sq.attn_causal(g["q"].cuda(), g["k"].cuda(), g["v"].cuda(), "HND", torch.float16, True, fp8)
+    _cmp(o, lse, g["o_fp8" if fp8 else "o"], g["lse_fp8" if fp8 else "lse"], tol_o=6e-3)
+
+
+def test_config2_blocks_32k(sq):
+    """32768 tokens, 28/4 heads, D=128 bf16 with outlier K channels and the reference's default window,
+    through the full operator (prep + kernel); the oracle is evaluated on a subset of 64-row query blocks."""
+    from longcontext_sqattn_paddle_b200.sqattn import mp_triton_wrapper
+    n, hq, hkv, d = 32768, 28, 4, 128
+    q, k, v = so.make_inputs(0, 1, n, hq, hkv, d, torch.bfloat16)
+
+    class Args:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", True
+
+    class Layer:
+        num_key_value_groups = hq // hkv
+
+    fn = mp_triton_wrapper(1, [0.1] * hq, [0.1] * hq, 256, Args())
+    out = fn(Layer(), q.cuda(), k.cuda(), v.cuda(), None).cpu()
+    blocks = [0, 1, 3, 4, 5, 77, 300, 510, 511]
+    ref = so.attention_fn(q, k, v, hq // hkv, [0.1] * hq, [0.1] * hq, 256, blocks=blocks)
+    rows = torch.cat([torch.arange(b * 64, b * 64 + 64) for b in blocks])
+    err = (out[:, rows].float() - ref[:, rows].float()).abs().max().item()
+    assert torch.isfinite(out).all() and err < TOL_O, err
+
+
+def test_errors(sq):
+    q = torch.zeros(1, 2, 128, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        sq.attn_hierarchical_relative_window(q, q, q, q, q, 0.1, 0.1, -1)
+    with pytest.raises(ValueError):
+        sq.attn_hierarchical_relative_window(q, q, q, q, q, 0.1, 0.1, 100)  # sink not a multiple of 64
+    big = torch.zeros(1, 2, 128, 256, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        sq.attn_causal(big, big, big)
+    with pytest.raises(ValueError):
+        sq.attn_causal(q, q, q, tensor_layout="XYZ")

@@ -1,0 +1,77 @@
+"""The fused input preparation (K centring + fake quantisers + q scaling) against the oracle's restatement of
+the adapter.  Integer grids make this almost always bit-exact; a value may land on the neighbouring grid point
+when the fp32 K mean differs in its last bit (different summation order), so a tiny fraction of mismatches by
+one quantisation step is allowed for K and none for Q and V."""
+import pytest
+import torch
+
+from oracle import sqattn_oracle as so
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n,hq,hkv,d", [(300, 4, 2, 128), (1024, 28, 4, 128), (77, 6, 3, 64)])
+@pytest.mark.parametrize("qk_qtype,v_qtype", [("int", "int"), ("e4m3", "e5m2"), ("e5m2", "e4m3")])
+def test_prep_matches_adapter(dtype, n, hq, hkv, d, qk_qtype, v_qtype):
+    from longcontext_sqattn_paddle_b200 import ops
+    q, k, v = so.make_inputs(3, 2, n, hq, hkv, d, dtype)
+    q8, q4, k8, k4, v8 = (t.cpu() for t in ops.prep_qkv(q.cuda(), k.cuda(), v.cuda(), qk_qtype=qk_qtype, v_qtype=v_qtype))
+    groups = hq // hkv
+    r8, r4, rk8, rk4, rv8 = so.prep_qkv(q, k, v, groups, qk_qtype, v_qtype)
+    r8, r4 = so.scale_q(r8, d), so.scale_q(r4, d)
+    rk8, rk4, rv8 = rk8[:, ::groups], rk4[:, ::groups], rv8[:, ::groups]
+    exact = qk_qtype == "int"
+
+    def frac_bad(a, b):
+        return (a.float() != b.float()).float().mean().item()
+
+    assert frac_bad(q4, r4) == 0 and frac_bad(k4, rk4) < 2e-3
+    if exact:
+        assert frac_bad(q8, r8) == 0
+        assert frac_bad(k8, rk8) < 2e-3
+    else:  # emulated float formats go through log2/exp2: compare by value
+        assert (q8.float() - r8.float()).abs().max().item() < 2e-2 * r8.float().abs().max().item()
+        assert frac_bad(q8, r8) < 1e-3 and frac_bad(k8, rk8) < 3e-3
+    if v_qtype == "int":
+        assert frac_bad(v8, rv8.to(torch.float16)) == 0
+    else:
+        assert frac_bad(v8, rv8.to(torch.float16)) < 1e-3
+    assert v8.dtype == torch.float16
+
+
+def test_operator_boundary():
+    """attention_fn installed with types.MethodType like the reference's process_model does."""
+    from longcontext_sqattn_paddle_b200.sqattn import process_model
+    hq, hkv, n, d = 8, 2, 700, 128
+
+    class Layer:
+        num_key_value_groups = hq // hkv
+
+        def prefill_attention(self, q, k, v, mask):
+            raise AssertionError("not replaced")
+
+    class Model:
+        layers = [Layer(), Layer(), Layer()]
+
+    class Args:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", True
+
+    model = process_model(Model(), "SQAttn", {1: {"bit8": [0.2] * hq, "bit4": [0.4] * hq, "sink": 256}}, Args())
+    q, k, v = so.make_inputs(5, 1, n, hq, hkv, d, torch.bfloat16)
+    out = model.layers[1].prefill_attention(q.cuda(), k.cuda(), v.cuda(), None)
+    assert out.shape == (1, n, hq * d) and out.dtype == torch.bfloat16
+    ref = so.attention_fn(q, k, v, hq // hkv, [0.2] * hq, [0.4] * hq, 256)
+    assert (out.float().cpu() - ref.float()).abs().max().item() < 2e-2
+    with pytest.raises(AssertionError):
+        model.layers[0].prefill_attention(q, k, v, None)
+    with pytest.raises(ValueError):
+        process_model(Model(), "Nope", {}, Args())
+
+    class AbsArgs:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", False
+
+    model = process_model(Model(), "SQAttn", {2: {"bit8": [128] * hq, "bit4": [256] * hq, "sink": 256}}, AbsArgs())
+    out = model.layers[2].prefill_attention(q.cuda(), k.cuda(), v.cuda(), None)
+    ref = so.attention_fn(q, k, v, hq // hkv, [128] * hq, [256] * hq, 256, use_relative_distance=False)
+    assert (out.float().cpu() - ref.float()).abs().max().item() < 2e-2
