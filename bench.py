@@ -1,0 +1,345 @@
+"""Benchmark of the SQAttn hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one call of the prefill operator (input preparation + windowed attention kernel, i.e.
+``layer.prefill_attention(q, k, v, None)``) on one batch of synthetic input with the shapes of the
+reference's 32K-token Qwen2.5-7B attention call: batch 1, 28 query / 4 KV heads, head_dim 128, bf16,
+Q,K,V ~ N(0,1) with four K channels scaled by 8, the reference's effective default window (sink 256,
+int8/int4 window ratio 0.1).  The metric is TFLOP/s counted over the (query, key) pairs the kernel has to
+visit (4*D flops per pair and head), never over padded tiles.  With N > 1 GPUs the sequence is N times
+longer and sharded by query blocks (sequence parallel, K/V all-gathered over NCCL): weak scaling.
+
+Prints ONE JSON line.  ``--impl reference`` times the CPU restatement of the reference's own path
+(oracle/) on the host cores instead, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+HQ, HKV, D = 28, 4, 128
+SEQ_PER_GPU = 32768
+SINK, RATIO = 256, 0.1
+
+
+# ----------------------------------------------------------------------------------------------- helpers
+def visited_pairs(n: int, w: int, sink: int) -> int:
+    """(query, key) pairs with non-zero weight per head for the relative-window schedule (BLOCK_M = 64)."""
+    total = 0
+    for qs in range(0, n, 64):
+        qe = qs + 64
+        l8 = max(sink, qe - w)
+        total += 64 * min(sink, qs)            # sink stage
+        if l8 < qs:
+            total += 64 * (qs - l8)            # window stage
+        total += 64 * 65 // 2                  # diagonal block
+    return total
+
+
+def window_size(ratio: float, kv_len: int) -> int:
+    raw = int((torch.tensor(ratio, dtype=torch.float32) * torch.tensor(float(kv_len), dtype=torch.float32)).item())
+    return (raw + 127) // 128 * 128
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"tflops": float(d["bf16_tflops"]), "hbm": float(d["hbm_gbs"]), "src": "measured"}
+    return {"tflops": 1590.0, "hbm": 6650.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) > 8:
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+def cpu_sample(seed: int, n: int, nblocks: int = 16, reps: int = 1):
+    """Time the oracle (the reference's fake-quant SQAttn path restated on CPU) on a bounded sample of the
+    workload: input preparation over a 4096-token slice (scaled to the full length: it is linear in tokens)
+    and `nblocks` of the n/64 query blocks for all 28 heads."""
+    from oracle import sqattn_oracle as so
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v = so.make_inputs(seed, 1, n, HQ, HKV, D, torch.bfloat16)
+    groups = HQ // HKV
+    sl = 4096
+    t0 = time.perf_counter()
+    so.prep_qkv(q[:, :sl], k[:, :sl], v[:, :sl], groups)
+    t_prep = (time.perf_counter() - t0) * (n / sl)
+    # kernel part on already prepared tensors (prep of the whole sequence is not repeated per block)
+    q8, _, k8, _, v8 = so.prep_qkv(q, k, v, 1)  # GQA-native: the kernel indexes KV heads itself
+    nblk = n // 64
+    step = max(1, nblk // nblocks)
+    blocks = list(range(step - 1, nblk, step))[:nblocks]
+    w = window_size(RATIO, n)
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        so.windowed_prefill(q8, k8, q8, k8, v8, [RATIO] * HQ, [RATIO] * HQ, SINK, mode="relative",
+                            output_dtype=torch.bfloat16, blocks=blocks)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    pairs = 0
+    for b in blocks:
+        qs, qe = b * 64, b * 64 + 64
+        l8 = max(SINK, qe - w)
+        pairs += 64 * min(SINK, qs) + (64 * (qs - l8) if l8 < qs else 0) + 64 * 65 // 2
+    flops = 4.0 * D * HQ * pairs
+    frac = len(blocks) / nblk
+    total_t = best + t_prep * frac
+    return {"value": flops / total_t / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{len(blocks)} of {nblk} 64-row query blocks x {HQ} heads at N={n} (tile kernel {best:.2f}s) + "
+                      f"the proportional share of input preparation ({t_prep:.2f}s for the full sequence, "
+                      f"timed on a {sl}-token slice)",
+            "seconds": total_t}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = SEQ_PER_GPU * args.gpus
+    vals = []
+    t_all = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        r = cpu_sample(i, n, nblocks=8)
+        if i >= args.warmup:
+            vals.append(r)
+    wall = time.perf_counter() - t_all
+    v = sum(x["value"] for x in vals) / len(vals)
+    ms = sum(x["seconds"] for x in vals) / len(vals) * 1e3
+    cb = dict(vals[-1]); cb["value"] = v; cb.pop("seconds", None)
+    out = {"impl": "reference", "metric": "sqattn_prefill_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": workload_config(n, args.gpus), "cpu_baseline": cb,
+           "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "wall_s": wall}
+    print(json.dumps(out))
+
+
+def workload_config(n, gpus):
+    return {"workload": f"SQAttn prefill operator, batch 1, {HQ} q / {HKV} kv heads, head_dim {D}, seq {n}, causal, bf16, "
+                        f"sink {SINK}, int8/int4 window ratio {RATIO} (the reference's effective default), K outlier channels x8",
+            "seq_len": n, "parallelism": f"sp{gpus}" if gpus > 1 else "single",
+            "l2": "inputs larger than L2 (Q alone is 235 MB per 32K tokens); no flush needed"}
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+
+    from longcontext_sqattn_paddle_b200 import ops
+    from longcontext_sqattn_paddle_b200 import _lib as L
+    from longcontext_sqattn_paddle_b200.sqattn.attn_replacer import mp_triton_wrapper
+    from oracle import sqattn_oracle as so
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_total = SEQ_PER_GPU * world
+    peaks = load_peaks()
+
+    class Args:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", True
+
+    class Layer:
+        num_key_value_groups = HQ // HKV
+
+    r = [RATIO] * HQ
+    if world == 1:
+        fn = mp_triton_wrapper(1, r, r, SINK, Args())
+        op = lambda q, k, v: fn(Layer(), q, k, v, None)
+        launches_per_step = 6
+    else:
+        from longcontext_sqattn_paddle_b200 import dist as sqdist
+        spfn = sqdist.sp_prefill_wrapper(r, r, SINK, Args(), seq_total=n_total)
+        op = lambda q, k, v: spfn(Layer(), q, k, v, None)
+        launches_per_step = 7
+
+    # synthetic input: this rank's 32K-token shard of the sequence, pinned on the host and resident in HBM
+    q, k, v = so.make_inputs(1000 + rank, 1, SEQ_PER_GPU, HQ, HKV, D, torch.bfloat16)
+    hq_, hk_, hv_ = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    dq, dk, dv = hq_.to(dev), hk_.to(dev), hv_.to(dev)
+    w = window_size(RATIO, n_total)
+    flops_total = 4.0 * D * HQ * visited_pairs(n_total, w, SINK)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn_, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn_()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    # ---- device-resident throughput
+    for _ in range(max(args.warmup, 3)):
+        out = op(dq, dk, dv)
+    ops.check_device_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: op(dq, dk, dv), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_device_status()
+    ms_per_step = ms / args.steps
+    value = flops_total / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host buffers in, host buffer out, copies inside the timed region
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        a, b_, c = hq_.to(dev, non_blocking=True), hk_.to(dev, non_blocking=True), hv_.to(dev, non_blocking=True)
+        hout.copy_(op(a, b_, c), non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    e2e = {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": out.numel() * 2}
+
+    # ---- roofline of the dominant kernel (the attention kernel alone, events on its stream)
+    roof = None
+    extra = {}
+    if world == 1:
+        q8, _, k8, _, v8 = ops.prep_qkv(dq, dk, dv, skip_bit4=True)
+        o4 = torch.empty(1, SEQ_PER_GPU, HQ, D, dtype=torch.bfloat16, device=dev)
+        kern = lambda: ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_RELATIVE_WINDOW, win8=r, win4=r, sink=SINK,
+                                   q_is_scaled=True, out=o4, out_layout="NHD")
+        for _ in range(3):
+            kern()
+        kms = timed(kern, args.steps) / args.steps
+        ach = flops_total / (kms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "prefill_kernel<128> (relative windows)", "achieved": ach,
+                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "peak_source": peaks["src"],
+                "ms_per_launch": kms, "traffic": None}
+        # dense causal on the same tensors: the tensor-core-bound configuration
+        dense = lambda: ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_DENSE_CAUSAL, q_is_scaled=True, out=o4, out_layout="NHD")
+        for _ in range(2):
+            dense()
+        dms = timed(dense, max(2, args.steps // 2)) / max(2, args.steps // 2)
+        dflops = 4.0 * D * HQ * (SEQ_PER_GPU * (SEQ_PER_GPU + 1) / 2)
+        extra["dense_causal"] = {"tflops": dflops / (dms * 1e-3) / 1e12, "ms": dms,
+                                 "frac_of_bf16_peak": dflops / (dms * 1e-3) / 1e12 / peaks["tflops"]}
+        # decode: one 1M-token layer (K and V 1 GiB each) streamed per launch, four such layers in rotation
+        try:
+            Lkv = 1 << 20
+            layers = [(torch.randn(1, HKV, Lkv, D, device=dev, dtype=torch.bfloat16),
+                       torch.randn(1, HKV, Lkv, D, device=dev, dtype=torch.bfloat16)) for _ in range(4)]
+            qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16)
+            state = {"i": 0}
+
+            def dec():
+                kk, vv = layers[state["i"] % 4]
+                state["i"] += 1
+                ops.decode(qd, kk, vv, out_dtype=torch.bfloat16)
+
+            for _ in range(4):
+                dec()
+            nl = 28
+            dms_ = timed(dec, nl) / nl
+            gbs = 2.0 * HKV * Lkv * D * 2 / (dms_ * 1e-3) / 1e9
+            extra["decode_1m"] = {"gb_per_s": gbs, "ms_per_layer": dms_, "frac_of_measured_hbm": gbs / peaks["hbm"],
+                                  "frac_of_8tbs": gbs / 8000.0, "bytes_per_launch": 2 * HKV * Lkv * D * 2}
+            del layers
+        except Exception as e:  # noqa: BLE001
+            extra["decode_1m"] = {"error": repr(e)}
+        ops.check_device_status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_sample(0, SEQ_PER_GPU, nblocks=16)
+        cpu.pop("seconds", None)
+
+    if rank == 0:
+        res = {"metric": "sqattn_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+               "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+               "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(n_total, world),
+               "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+               "roofline": roof, "cpu_baseline": cpu}
+        res.update(extra)
+        print(json.dumps(res))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -127,6 +127,8 @@ typedef struct {
   int32_t p_fp8;           /* is_P_fp8_quant */
   int32_t q_is_scaled;     /* 0: the kernel applies 1/sqrt(D)*1.44269504 in q's dtype on load */
   int32_t num_splits;      /* 0 = let the length-aware scheduler choose */
+  int32_t reference_tail;  /* 1: like the reference kernel (attn_triton_decode.py:215-221), positions between kv_len
+                              and the next multiple of 64 count as keys with score 0 and value 0; 0: exact masking */
   void* workspace;         /* device scratch, sqattn_decode_workspace_bytes() bytes */
   size_t workspace_bytes;
   /* multi-GPU split-KV: when partial_o != NULL the merge is skipped and the per-sequence partial

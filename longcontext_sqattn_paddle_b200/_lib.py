@@ -62,7 +62,7 @@ class DecodeArgs(C.Structure):
         ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("kv_len", C.c_int32), ("kv_lens", C.POINTER(C.c_int32)),
         ("dtype", C.c_int32), ("o_dtype", C.c_int32), ("p_fp8", C.c_int32), ("q_is_scaled", C.c_int32),
-        ("num_splits", C.c_int32),
+        ("num_splits", C.c_int32), ("reference_tail", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p),
     ]

@@ -27,6 +27,7 @@ struct DecodeParams {
   int batch, hq, hkv, groups, d;
   int chunk;  // keys per work item (multiple of 64)
   int p_fp8, q_is_scaled;
+  int reference_tail;  // keys between a sequence's length and the next multiple of 64 count with score 0
   float sm_scale;  // 1/sqrt(D) * 1.44269504 evaluated in double on the host, like the Python launcher
   int lens[kDecMaxBatch];
   int item_prefix[kDecMaxBatch + 1];  // first work item of each sequence
@@ -101,8 +102,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int bi = lo;
   const int len = p.lens[bi];
   const int key_begin = (item - p.item_prefix[bi]) * p.chunk;
-  const int key_end = min(len, key_begin + p.chunk);
-  const int ntiles = (key_end - key_begin + kDecTile - 1) / kDecTile;
+  const int key_end = min(len, key_begin + p.chunk);  // real keys
+  // The reference kernel loads keys past kv_len as zeros without masking their scores (masked tl.load,
+  // attn_triton_decode.py:215-221), so its last 64-key tile is padded with keys of score 0 and value 0.
+  const int proc_end = p.reference_tail ? min((len + kDecTile - 1) / kDecTile * kDecTile, key_begin + p.chunk) : key_end;
+  const int ntiles = (proc_end - key_begin + kDecTile - 1) / kDecTile;
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
@@ -167,11 +171,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       if (!ok) break;
       const uint32_t k_tile = sbase + st * L::kStageBytes, v_tile = k_tile + L::kTileBytes;
       const int key0 = key_begin + t * kDecTile + wk;  // first key of this warp
-      if (key0 < key_end) {
+      if (key0 < proc_end) {
         // rows past the end of the sequence may hold anything (the cache is larger than the sequence):
-        // their scores are masked below, and their V rows are zeroed so that 0 * garbage cannot make a NaN
+        // their scores are overwritten below, and their V rows are zeroed so that 0 * garbage cannot make a NaN
         if (key0 + 16 > key_end) {
-          for (int r = key_end - key0; r < 16; ++r)
+          for (int r = max(0, key_end - key0); r < 16; ++r)
             for (int c = lane; c < D / 8; c += 32)
               *reinterpret_cast<uint4*>(smem + st * L::kStageBytes + L::kTileBytes + tile_off(wk + r, c)) =
                   make_uint4(0, 0, 0, 0);
@@ -194,7 +198,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int key = key0 + nb * 8 + tq * 2 + (e & 1);
-            if (key >= key_end) s[nb][e] = -INFINITY;
+            if (key >= key_end) s[nb][e] = (key < proc_end) ? 0.f : -INFINITY;
             mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
           }
         float alpha[2];

@@ -44,12 +44,12 @@ struct PrefillParams {
 
 // Key ranges of the four stages for the query block [qs, qe)
 // (attn_triton_mix_relative.py:36-75, attn_triton_mix_bad.py:41-74).
-__device__ __forceinline__ void stage_range(int stage, int qs, int qe, int w8, int w4, int sink, int& lo, int& hi) {
-  const int l4 = max(sink, qe - w4);
-  const int l8 = max(sink, qe - w8);
+__host__ __device__ __forceinline__ void stage_range(int stage, int qs, int qe, int w8, int w4, int sink, int& lo, int& hi) {
+  const int l4 = sink > qe - w4 ? sink : qe - w4;
+  const int l8 = sink > qe - w8 ? sink : qe - w8;
   lo = hi = 0;
   if (stage == 1) {
-    hi = min(sink, qs);
+    hi = sink < qs ? sink : qs;
   } else if (stage == 2) {
     if (l4 < l8) { lo = l4; hi = l8; }
   } else if (stage == 3) {
@@ -63,7 +63,7 @@ __device__ __forceinline__ void stage_range(int stage, int qs, int qe, int w8, i
 // 128 rows.  The relative-window mode has BLOCK_M = 64: the CTA covers two reference blocks whose stage
 // ranges are offset by 0 or 64 keys; their tiles are merged stage by stage and each step records which
 // half takes part, so every half sees exactly its own tiles in the reference order.
-__device__ int build_schedule(Seg* segs, const PrefillParams& p, int blk, int head) {
+__host__ __device__ inline int build_schedule(Seg* segs, const PrefillParams& p, int blk, int head) {
   int n = 0;
   const int stage_flags_fp8_all = (p.p_fp8_mode == 1) ? kSegFp8 : 0;
   auto flags_of = [&](int stage) {
@@ -100,8 +100,8 @@ __device__ int build_schedule(Seg* segs, const PrefillParams& p, int blk, int he
     if (has1) stage_range(stage, qs1, qs1 + 64, w8, w4, p.sink, lo1, hi1);
     const bool e0 = hi0 <= lo0, e1 = hi1 <= lo1;
     if (e0 && e1) continue;
-    const int lo = e0 ? lo1 : (e1 ? lo0 : min(lo0, lo1));
-    const int hi = e0 ? hi1 : (e1 ? hi0 : max(hi0, hi1));
+    const int lo = e0 ? lo1 : (e1 ? lo0 : (lo0 < lo1 ? lo0 : lo1));
+    const int hi = e0 ? hi1 : (e1 ? hi0 : (hi0 > hi1 ? hi0 : hi1));
     int run_start = 0, run_act = -1, run_len = 0;
     for (int t = lo; t < hi; t += kBlockN) {
       const int act = ((!e0 && t >= lo0 && t < hi0) ? kSegAct0 : 0) | ((!e1 && t >= lo1 && t < hi1) ? kSegAct1 : 0);
@@ -127,8 +127,8 @@ struct PrefillSmem {
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kVOff = kKOff + kKStages * kKBytes;
   static constexpr int kBarOff = kVOff + kVStages * kVBytes;
-  // barriers: q_full, q_empty, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], o_done
-  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 1;
+  // barriers: q_full, q_empty, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], o_done[2]
+  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
   static constexpr int kSegOff = kMiscOff + 16;  // tmem base, abort flag, nseg
   static constexpr int kTotal = kSegOff + kMaxSegs * 12;
@@ -200,6 +200,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     for (int i = 0; i < VS; ++i) { mbar_init(bar_v_full + 8 * i, 1); mbar_init(bar_v_empty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(bar_s_full + 8 * i, 1); mbar_init(bar_p_full + 8 * i, 128); }
     mbar_init(bar_o_done, 1);
+    mbar_init(bar_o_done + 8, 1);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -299,7 +300,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
                  idesc_pv, (i > 0 || kk > 0));
         }
         tc_commit(bar_v_empty + 8 * vs);
-        tc_commit(bar_o_done);
+        // two alternating barriers: a waiter that is up to two steps behind the tensor pipe can still tell the
+        // phases apart by parity
+        tc_commit(bar_o_done + 8 * (i & 1));
       }
     }
   } else {
@@ -362,7 +365,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       // acc *= alpha: O lives in TMEM and is rescaled only when some row of this warp moved its maximum
       // (alpha == 1 exactly otherwise, so skipping is bit-identical).
       if (__any_sync(0xffffffffu, alpha != 1.0f) && i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_o_done, (i - 1) & 1, cta_abort, 122));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_o_done + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, cta_abort, 122));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
@@ -379,7 +382,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * (i & 1));
     }
-    if (ok && nsteps > 0) ok = mbar_wait(bar_o_done, (nsteps - 1) & 1, cta_abort, 123);
+    if (ok && nsteps > 0) ok = mbar_wait(bar_o_done + 8 * ((nsteps - 1) & 1), ((nsteps - 1) >> 1) & 1, cta_abort, 123);
     ok = __all_sync(0xffffffffu, ok);
     if (ok && nsteps > 0) {
       tc_fence_after();

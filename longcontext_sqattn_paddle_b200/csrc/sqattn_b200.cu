@@ -244,7 +244,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   p.part_o = reinterpret_cast<float*>(ws);
   p.part_lse = reinterpret_cast<float*>(ws + align_up(rows * D * 4, 256));
   p.batch = a->batch; p.hq = a->num_q_heads; p.hkv = a->num_kv_heads; p.groups = a->num_q_heads / a->num_kv_heads; p.d = D;
-  p.chunk = pl.chunk; p.p_fp8 = a->p_fp8; p.q_is_scaled = a->q_is_scaled;
+  p.chunk = pl.chunk; p.p_fp8 = a->p_fp8; p.q_is_scaled = a->q_is_scaled; p.reference_tail = a->reference_tail;
   p.sm_scale = static_cast<float>(sm_scale_log2(D));
   memcpy(p.lens, pl.lens, sizeof(int) * a->batch);
   memcpy(p.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
@@ -288,6 +288,17 @@ int sqattn_prefill(const sqattn_prefill_args* args, sqattn_stream_t stream) {
 }
 
 #ifdef SQATTN_DEBUG_EXPORTS
+// Debug builds only: the step list of one CTA, computed on the host (out: up to 12 x {start, ntiles, flags}).
+int sqattn_debug_schedule(int mode, int n, int sink, int w8, int w4, int p_fp8_mode, int same_opset, int blk, int* out) {
+  PrefillParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = mode; p.n = n; p.kv_len = n; p.sink = sink; p.p_fp8_mode = p_fp8_mode; p.same_opset = same_opset;
+  p.w8[0] = w8; p.w4[0] = w4;
+  Seg segs[kMaxSegs];
+  const int ns = build_schedule(segs, p, blk, 0);
+  for (int i = 0; i < ns; ++i) { out[3 * i] = segs[i].start; out[3 * i + 1] = segs[i].ntiles; out[3 * i + 2] = segs[i].flags; }
+  return ns;
+}
 // Debug builds only: same as sqattn_prefill, and CTA 0 additionally writes every S tile it sees
 // ([steps][128 rows][64 keys] fp32) to `dump`.
 int sqattn_debug_prefill_dump(const sqattn_prefill_args* args, float* dump, sqattn_stream_t stream) {

@@ -123,9 +123,10 @@ def prep_qkv(query, key, value, *, qk_qtype: str = "int", v_qtype: str = "int", 
 
 def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse: bool = False, p_fp8: bool = False,
            q_is_scaled: bool = False, kv_lens: Optional[Sequence[int]] = None, kv_len: Optional[int] = None,
-           num_splits: int = 0, partial: bool = False):
+           num_splits: int = 0, partial: bool = False, reference_tail: bool = False):
     """sqattn_decode.  q [B,Hq,1,D] (HND) or [B,1,Hq,D] (NHD); k/v caches of capacity >= kv_len.
-    partial=True returns (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of these keys for a later merge."""
+    partial=True returns (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of these keys for a later merge.
+    reference_tail=True reproduces the reference kernel's zero-score padding of the last 64-key tile."""
     _require_cuda(q, k, v)
     b, hq, one, d = _shape(q, layout)
     assert one == 1
@@ -139,6 +140,7 @@ def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse:
         lens = (C.c_int32 * b)(*[int(x) for x in kv_lens])
         a.kv_lens = lens
     a.dtype, a.p_fp8, a.q_is_scaled, a.num_splits = _dt(k.dtype), int(p_fp8), int(q_is_scaled), int(num_splits)
+    a.reference_tail = int(reference_tail)
     out = lse = po = pl = None
     if partial:
         po = torch.empty(b, hq, d, dtype=torch.float32, device=q.device)

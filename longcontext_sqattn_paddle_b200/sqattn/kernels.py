@@ -103,5 +103,5 @@ def attn_unified(q, k, v, tensor_layout="HND", output_dtype=torch.float16, retur
         k = k - km
     if q.shape[seq_dim] == 1:
         return ops.decode(q, k, v, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
-                          p_fp8=is_P_fp8_quant, kv_lens=kv_lens)
+                          p_fp8=is_P_fp8_quant, kv_lens=kv_lens, reference_tail=True)
     return attn_causal(q, k, v, tensor_layout, output_dtype, return_lse, is_P_fp8_quant)

@@ -398,7 +398,8 @@ def dense_causal(q, k, v, *, tensor_layout: str = "HND", output_dtype=torch.floa
 
 def decode(q, k, v, *, tensor_layout: str = "HND", output_dtype=torch.float16, return_lse: bool = False,
            is_P_fp8_quant: bool = False, center_k: bool = True, block_n: int = 64,
-           kv_lens: Optional[Sequence[int]] = None, qk_in_input_dtype: bool = False):
+           kv_lens: Optional[Sequence[int]] = None, qk_in_input_dtype: bool = False,
+           mask_tail: bool = False):
     """Single-query attention, attn_unified decode branch + _attn_decode_fwd
     (attn_triton_decode.py:175-241, 244-361): K re-centred over the sequence
     (268-269), q scaled in its dtype (270-271), 64-key online softmax with
@@ -406,7 +407,11 @@ def decode(q, k, v, *, tensor_layout: str = "HND", output_dtype=torch.float16, r
     ``kv_lens`` (one per batch row) extends it to ragged batches: rows at or
     beyond a sequence's length are masked like the kernel's kv_len mask.
     ``qk_in_input_dtype`` rounds each q*k product to the input dtype as the
-    Triton elementwise multiply does (221); accumulation stays fp32."""
+    Triton elementwise multiply does (221); accumulation stays fp32.
+    The reference loads keys past kv_len as zeros and does not mask their
+    scores (215-221): the last tile is padded with keys of score 0 and value
+    0, which this function reproduces; ``mask_tail=True`` masks them instead
+    (exact softmax over the real keys, an option the CUDA path also has)."""
     (q, k, v), d_og = _pad_head_dim([q, k, v])
     qh, kh, vh = _as_hnd(q, tensor_layout), _as_hnd(k, tensor_layout), _as_hnd(v, tensor_layout)
     b, h, one, d = qh.shape
@@ -437,6 +442,8 @@ def decode(q, k, v, *, tensor_layout: str = "HND", output_dtype=torch.float16, r
                 qk = prod.sum(-1)
             else:
                 qk = torch.einsum("hd,hnd->hn", qv.float(), k_t.float())
+            if mask_tail and start_n + block_n > L:
+                qk[:, L - start_n:] = float("-inf")
             m_ij = torch.maximum(m_i, qk.max(dim=-1).values)
             p = torch.exp2(qk - m_ij[:, None])
             l_ij = p.sum(-1)

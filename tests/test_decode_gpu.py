@@ -29,10 +29,13 @@ def _rand(shape, seed, dtype):
 @pytest.mark.parametrize("b,hq,hkv,L,d", [(1, 28, 4, 5000, 128), (2, 4, 2, 600, 64), (3, 32, 8, 1, 128),
                                           (1, 8, 1, 64, 128), (2, 16, 1, 20000, 128)])
 @pytest.mark.parametrize("fp8", [False, True])
-def test_decode(ops, dtype, b, hq, hkv, L, d, fp8):
+@pytest.mark.parametrize("ref_tail", [True, False])
+def test_decode(ops, dtype, b, hq, hkv, L, d, fp8, ref_tail):
     q, k, v = _rand((b, hq, 1, d), 1, dtype), _rand((b, hkv, L, d), 2, dtype), _rand((b, hkv, L, d), 3, dtype)
-    o, lse = ops.decode(q.cuda(), k.cuda(), v.cuda(), out_dtype=dtype, return_lse=True, p_fp8=fp8)
-    ro, rlse = so.decode(q, k, v, output_dtype=dtype, return_lse=True, is_P_fp8_quant=fp8, center_k=False)
+    o, lse = ops.decode(q.cuda(), k.cuda(), v.cuda(), out_dtype=dtype, return_lse=True, p_fp8=fp8,
+                        reference_tail=ref_tail)
+    ro, rlse = so.decode(q, k, v, output_dtype=dtype, return_lse=True, is_P_fp8_quant=fp8, center_k=False,
+                         mask_tail=not ref_tail)
     assert torch.isfinite(o).all()
     assert (o.float().cpu() - ro.float()).abs().max().item() < 2e-2
     assert (lse.cpu() - rlse).abs().max().item() < 2e-3
@@ -49,7 +52,7 @@ def test_decode_ragged_nhd(ops):
         v[i, n:] = float("nan")
     o = ops.decode(q.cuda(), k.cuda(), v.cuda(), layout="NHD", out_dtype=dtype, kv_lens=lens)
     ro = so.decode(q, torch.nan_to_num(k), torch.nan_to_num(v), tensor_layout="NHD", output_dtype=dtype,
-                   center_k=False, kv_lens=lens)
+                   center_k=False, kv_lens=lens, mask_tail=True)
     assert torch.isfinite(o).all()
     assert (o.float().cpu() - ro.float()).abs().max().item() < 2e-2
 
