@@ -327,6 +327,49 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_kernel_only(args):
+    """A few launches of one kernel on the bench's tensors: the command profiler captures are taken on."""
+    from longcontext_sqattn_paddle_b200 import _lib as L
+    from longcontext_sqattn_paddle_b200 import ops
+    from oracle import sqattn_oracle as so
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = args.seq
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.kernel_only == "decode":
+        kk = torch.randn(1, HKV, n, D, device=dev, dtype=torch.bfloat16)
+        vv = torch.randn(1, HKV, n, D, device=dev, dtype=torch.bfloat16)
+        qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.decode(qd, kk, vv, out_dtype=torch.bfloat16)
+        work, unit = 2.0 * HKV * n * D * 2 / 1e9, "GB/s"
+    else:
+        q, k, v = so.make_inputs(1000, 1, n, HQ, HKV, D, torch.bfloat16)
+        q8, _, k8, _, v8 = ops.prep_qkv(q.to(dev), k.to(dev), v.to(dev), skip_bit4=True)
+        o4 = torch.empty(1, n, HQ, D, dtype=torch.bfloat16, device=dev)
+        r = [RATIO] * HQ
+        if args.kernel_only == "prefill":
+            fn = lambda: ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_RELATIVE_WINDOW, win8=r, win4=r, sink=SINK,
+                                     q_is_scaled=True, out=o4, out_layout="NHD")
+            work = 4.0 * D * HQ * visited_pairs(n, window_size(RATIO, n), SINK) / 1e12
+        else:
+            fn = lambda: ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_DENSE_CAUSAL, q_is_scaled=True, out=o4,
+                                     out_layout="NHD")
+            work = 4.0 * D * HQ * (n * (n + 1) / 2) / 1e12
+        unit = "TFLOP/s"
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"kernel": args.kernel_only, "seq": n, "ms_per_launch": ms, "rate": work / (ms * 1e-3), "unit": unit}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -334,8 +377,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode"],
+                    help="launch only this kernel --steps times on the bench tensors (for profiler captures)")
+    ap.add_argument("--seq", type=int, default=SEQ_PER_GPU, help="sequence length for --kernel-only")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel_only:
+        run_kernel_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -1,6 +1,8 @@
 """Build libsqattn_b200.so in-tree with nvcc for sm_100a.
 
-    python -m longcontext_sqattn_paddle_b200.build [--debug-exports]
+    python longcontext_sqattn_paddle_b200/build.py [--force] [--debug-exports]
+
+(run as a script: it must work before the package itself can be imported)
 """
 from __future__ import annotations
 
