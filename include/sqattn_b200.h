@@ -143,6 +143,22 @@ typedef struct {
 size_t sqattn_decode_workspace_bytes(const sqattn_decode_args* args);
 int sqattn_decode(const sqattn_decode_args* args, sqattn_stream_t stream);
 
+/* No counterpart in the reference.  Same computation and results as sqattn_decode, for callers that cannot
+ * give it a workspace because they may not allocate device memory where they call from: code running inside
+ * a framework's memory-planned region or a serving loop with a frozen memory pool, where a cudaMalloc (or a
+ * caching allocator growing its pool) would synchronise the device or is forbidden outright.  The split-KV
+ * partials go to a scratch array built into the library (4 MiB + 64 KiB per GPU that loads the library, held
+ * until the process exits); args->workspace and workspace_bytes are ignored.  Limits and rules:
+ *  - the call is rejected with SQATTN_ERR_WORKSPACE when (key ranges x query heads) partial rows need more than
+ *    that (at head_dim 128: 8192 rows, e.g. 292 key ranges of 28 heads); nothing is launched in that case;
+ *  - it calls no cudaMalloc/cudaFree and no allocating library routine;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress) with that device
+ *    current; make that first call before any stream capture begins;
+ *  - all calls on a device share the one array, which keeps the previous call's contents (nothing in it has to
+ *    start at zero: every partial row is written before the merge reads it); two calls that overlap on the GPU
+ *    (different streams) race on it -- serialise them. */
+int sqattn_decode_static_scratch(const sqattn_decode_args* args, sqattn_stream_t stream);
+
 /* Merge num_parts partial results laid out [num_parts, rows, D] / [num_parts, rows] (e.g. the
  * all-gathered per-GPU partials): O = sum 2^(lse_i-max) O_i / sum 2^(lse_i-max).  rows = B*Hq. */
 int sqattn_decode_merge(const float* partial_o, const float* partial_lse, int32_t num_parts, int64_t rows,

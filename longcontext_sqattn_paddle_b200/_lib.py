@@ -76,6 +76,7 @@ SYMBOLS = [
     ("sqattn_prep_qkv", C.c_int, [C.POINTER(PrepArgs), C.c_void_p]),
     ("sqattn_decode_workspace_bytes", C.c_size_t, [C.POINTER(DecodeArgs)]),
     ("sqattn_decode", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    ("sqattn_decode_static_scratch", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     ("sqattn_decode_merge", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32,
                                       C.c_void_p, C.c_void_p]),
     ("sqattn_kmeans_assign", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
@@ -97,11 +98,15 @@ SYMBOLS = [
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()' or "
-        "python -m longcontext_sqattn_paddle_b200.build). There is no CPU or PyTorch fallback.")
+        "python longcontext_sqattn_paddle_b200/build.py). There is no CPU or PyTorch fallback.")
 
 lib = C.CDLL(LIB_PATH)
 for _name, _res, _args in SYMBOLS:
-    _fn = getattr(lib, _name)
+    try:
+        _fn = getattr(lib, _name)
+    except AttributeError as exc:
+        raise ImportError(f"{LIB_PATH} is stale (no symbol {_name}): rebuild it with "
+                          "python longcontext_sqattn_paddle_b200/build.py --force") from exc
     _fn.restype = _res
     _fn.argtypes = _args
 

@@ -391,6 +391,48 @@ int sqattn_decode_merge(const float* partial_o, const float* partial_lse, int32_
   return SQATTN_OK;
 }
 
+// ---- decode for callers that cannot hand over scratch memory ---------------------------------------------
+// Scratch for the split-KV partials lives in this file-scope device array instead of a caller workspace.
+// Every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = (4u << 20) + (64u << 10);  // 4 MiB of partial O + 64 KiB of partial LSE
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle; its device address has to be asked for, once per device and
+// with that device current.
+static int static_scratch_address(void** out) {
+  static void* table[64] = {nullptr};
+  int dev = 0;
+  SQ_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SQATTN_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (!table[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(SQATTN_ERR_CUDA, "cudaGetSymbolAddress(g_decode_static_scratch): %s", cudaGetErrorString(e));
+    table[dev] = ptr;
+  }
+  *out = table[dev];
+  return SQATTN_OK;
+}
+
+int sqattn_decode_static_scratch(const sqattn_decode_args* args, sqattn_stream_t stream) {
+  DecodePlan pl;
+  int rc = plan_decode(args, &pl);
+  if (rc) return rc;
+  const size_t need = decode_ws_bytes(args, pl);
+  if (need > kStaticScratchBytes)
+    return fail(SQATTN_ERR_WORKSPACE,
+                "this call needs %zu bytes of scratch (%d key ranges x %d query heads) but the built-in scratch holds "
+                "%zu: fewer sequences or splits, or sqattn_decode with a caller workspace",
+                need, pl.total_items, args->num_q_heads, kStaticScratchBytes);
+  void* ptr = nullptr;
+  if ((rc = static_scratch_address(&ptr))) return rc;
+  sqattn_decode_args a = *args;
+  a.workspace = ptr;
+  a.workspace_bytes = kStaticScratchBytes;
+  return sqattn_decode(&a, stream);
+}
+
 // ---- kmeans ------------------------------------------------------------------------------------------
 #define SQ_KM_DISPATCH(KERNEL, ...)                                         \
   do {                                                                      \

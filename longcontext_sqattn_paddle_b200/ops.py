@@ -181,3 +181,28 @@ def decode_merge(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype=torch.f
 def check_device_status():
     """Raise if a bounded device-side wait gave up since the last check (synchronises the stream)."""
     L.check(L.lib.sqattn_check_device_status(_stream()))
+
+
+def decode_static_scratch(q, k, v, out, *, layout: str = "HND", lse: Optional[torch.Tensor] = None,
+                          p_fp8: bool = False, q_is_scaled: bool = False, kv_lens: Optional[Sequence[int]] = None,
+                          kv_len: Optional[int] = None, num_splits: int = 0, reference_tail: bool = False):
+    """sqattn_decode_static_scratch: decode into the caller's ``out`` (and ``lse``) without any allocation, for
+    callers inside a region where device memory may not be allocated.  The split-KV partials use the scratch
+    array built into the library (4 MiB + 64 KiB); calls that need more are rejected, and calls must not overlap
+    on the GPU.  Make the first call on a device outside stream capture."""
+    _require_cuda(q, k, v, out)
+    b, hq, one, d = _shape(q, layout)
+    assert one == 1
+    _, hkv, cap, _ = _shape(k, layout)
+    a = L.DecodeArgs()
+    a.q, a.k, a.v, a.o = _view(q, layout), _view(k, layout), _view(v, layout), _view(out, layout)
+    a.lse = None if lse is None else lse.data_ptr()
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = b, hq, hkv, d
+    a.kv_len = int(cap if kv_len is None else kv_len)
+    if kv_lens is not None:
+        lens = (C.c_int32 * b)(*[int(x) for x in kv_lens])
+        a.kv_lens = lens
+    a.dtype, a.o_dtype = _dt(k.dtype), _dt(out.dtype)
+    a.p_fp8, a.q_is_scaled, a.num_splits, a.reference_tail = int(p_fp8), int(q_is_scaled), int(num_splits), int(reference_tail)
+    L.check(L.lib.sqattn_decode_static_scratch(C.byref(a), _stream()))
+    return out
