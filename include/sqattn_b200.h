@@ -78,6 +78,8 @@ typedef struct {
                           launchers do, mix_relative.py:383-385) into the workspace; 1: caller already did */
   void* workspace;     /* device scratch, sqattn_prefill_workspace_bytes() bytes, 1024-byte aligned */
   size_t workspace_bytes;
+  int32_t q_row_offset; /* sequence-parallel shards: q/o hold rows [q_row_offset, q_row_offset + qo_len) of a
+                           kv_len-token sequence (multiple of 128); 0 for a whole sequence */
 } sqattn_prefill_args;
 
 /* Replaces the launch halves of attn_causal / attn_hierarchical_relative_window /
@@ -105,6 +107,10 @@ typedef struct {
   int32_t skip_bit4;         /* 1: q_bit4/k_bit4 are not needed (not written) */
   void* workspace;           /* device scratch, sqattn_prep_workspace_bytes() bytes (K column sums) */
   size_t workspace_bytes;
+  const float* k_mean;       /* optional device [B, Hkv, D] fp32: use this sequence mean of K instead of computing
+                                it (sequence-parallel shards pass the mean of the whole sequence) */
+  int32_t kv_out_nhd;        /* 1: k_bit8/k_bit4/v_bit8 are written token-major [B, N, Hkv, D] (so that shards
+                                all-gather into one contiguous tensor); 0: [B, Hkv, N, D] */
 } sqattn_prep_args;
 
 /* Replaces attention_fn's input preparation, sqattn/attn_replacer.py:334-365:
@@ -112,6 +118,13 @@ typedef struct {
  * per-(token,channel) fake-quant of V (sqattn/fake_quant.py:23-125, 151-248). */
 size_t sqattn_prep_workspace_bytes(const sqattn_prep_args* args);
 int sqattn_prep_qkv(const sqattn_prep_args* args, sqattn_stream_t stream);
+
+/* Column sums of K over the sequence, sums[b, h, d] = sum_n k[b, h, n, d] in fp32 (deterministic order): the
+ * first half of key.mean(dim=2) (sqattn/attn_replacer.py:338), split out so that sequence-parallel shards can
+ * all-reduce their sums.  workspace: batch * num_kv_heads * 64 * head_dim floats. */
+int sqattn_k_column_sums(const sqattn_tensor* k, int32_t batch, int32_t num_kv_heads, int32_t seq_len,
+                         int32_t head_dim, int32_t dtype, float* sums, void* workspace, size_t workspace_bytes,
+                         sqattn_stream_t stream);
 
 /* ---- decode ------------------------------------------------------------------------------- */
 

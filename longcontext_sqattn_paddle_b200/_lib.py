@@ -41,6 +41,7 @@ class PrefillArgs(C.Structure):
         ("win8_sizes", C.POINTER(C.c_int32)), ("win4_sizes", C.POINTER(C.c_int32)),
         ("p_fp8_mode", C.c_int32), ("q_is_scaled", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_row_offset", C.c_int32),
     ]
 
 
@@ -53,6 +54,7 @@ class PrepArgs(C.Structure):
         ("head_dim", C.c_int32), ("dtype", C.c_int32), ("qk_qtype", C.c_int32), ("v_qtype", C.c_int32),
         ("round_half_even", C.c_int32), ("skip_bit4", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("k_mean", C.c_void_p), ("kv_out_nhd", C.c_int32),
     ]
 
 
@@ -74,6 +76,8 @@ SYMBOLS = [
     ("sqattn_prefill", C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
     ("sqattn_prep_workspace_bytes", C.c_size_t, [C.POINTER(PrepArgs)]),
     ("sqattn_prep_qkv", C.c_int, [C.POINTER(PrepArgs), C.c_void_p]),
+    ("sqattn_k_column_sums", C.c_int, [C.POINTER(Tensor), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("sqattn_decode_workspace_bytes", C.c_size_t, [C.POINTER(DecodeArgs)]),
     ("sqattn_decode", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     ("sqattn_decode_static_scratch", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),

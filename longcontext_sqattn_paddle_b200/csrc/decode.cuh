@@ -313,7 +313,16 @@ struct MergeParams {
 };
 
 // O = sum_i 2^(lse_i - max) O_i / sum_i 2^(lse_i - max);  lse = log2(sum) + max
-__global__ void decode_merge_kernel(const __grid_constant__ MergeParams p) {
+// One CTA per output row (b, h).  The partial weights are computed once into shared memory; the partials are
+// then summed by kMergeGroups thread groups in parallel (each takes every kMergeGroups-th partial, four loads
+// in flight per thread) and the groups are combined in a fixed order, so the result does not depend on timing.
+constexpr int kMergeGroups = 4;
+constexpr int kMergeMaxParts = 2048;
+
+__global__ void __launch_bounds__(128 * kMergeGroups) decode_merge_kernel(const __grid_constant__ MergeParams p) {
+  __shared__ float w_s[kMergeMaxParts];
+  __shared__ float red_s[kMergeGroups][128];
+  __shared__ float max_s[32];
   const long long row = blockIdx.x;  // b*hq + h
   const int b = static_cast<int>(row / p.hq), h = static_cast<int>(row % p.hq);
   int first = 0, count = p.num_parts;
@@ -325,16 +334,48 @@ __global__ void decode_merge_kernel(const __grid_constant__ MergeParams p) {
     part_stride = p.hq;
     base_row = static_cast<long long>(first) * p.hq + h;
   }
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  float mloc = -INFINITY;
+  for (int i = tid; i < count; i += nthr) mloc = fmaxf(mloc, p.part_lse[base_row + i * part_stride]);
+  for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+  if ((tid & 31) == 0) max_s[tid >> 5] = mloc;
+  __syncthreads();
   float mmax = -INFINITY;
-  for (int i = 0; i < count; ++i) mmax = fmaxf(mmax, p.part_lse[base_row + i * part_stride]);
-  for (int col = threadIdx.x; col < p.d; col += blockDim.x) {
-    float acc = 0.f, den = 0.f;
-    for (int i = 0; i < count; ++i) {
-      const float lse_i = p.part_lse[base_row + i * part_stride];
-      const float w = (lse_i == -INFINITY) ? 0.f : exp2f(lse_i - mmax);
-      den += w;
-      acc += w * p.part_o[(base_row + i * part_stride) * p.d + col];
+  for (int i = 0; i < (nthr + 31) / 32; ++i) mmax = fmaxf(mmax, max_s[i]);
+  float den = 0.f;
+  for (int base = 0; base < count; base += kMergeMaxParts) {  // more than kMergeMaxParts partials: in rounds
+    const int cnt = min(kMergeMaxParts, count - base);
+    __syncthreads();
+    for (int i = tid; i < cnt; i += nthr) {
+      const float lse_i = p.part_lse[base_row + (base + i) * part_stride];
+      w_s[i] = (lse_i == -INFINITY) ? 0.f : exp2f(lse_i - mmax);
     }
+    __syncthreads();
+    for (int i = 0; i < cnt; ++i) den += w_s[i];  // same order in every thread
+    const int col = tid % 128, grp = tid / 128;
+    if (col < p.d) {
+      float acc = (base == 0) ? 0.f : red_s[grp][col];
+      int i = grp;
+      for (; i + 3 * kMergeGroups < cnt; i += 4 * kMergeGroups) {
+        const float v0 = p.part_o[(base_row + (base + i) * part_stride) * p.d + col];
+        const float v1 = p.part_o[(base_row + (base + i + kMergeGroups) * part_stride) * p.d + col];
+        const float v2 = p.part_o[(base_row + (base + i + 2 * kMergeGroups) * part_stride) * p.d + col];
+        const float v3 = p.part_o[(base_row + (base + i + 3 * kMergeGroups) * part_stride) * p.d + col];
+        acc += w_s[i] * v0;
+        acc += w_s[i + kMergeGroups] * v1;
+        acc += w_s[i + 2 * kMergeGroups] * v2;
+        acc += w_s[i + 3 * kMergeGroups] * v3;
+      }
+      for (; i < cnt; i += kMergeGroups) acc += w_s[i] * p.part_o[(base_row + (base + i) * part_stride) * p.d + col];
+      red_s[grp][col] = acc;
+    }
+  }
+  __syncthreads();
+  if (tid < p.d) {
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < kMergeGroups; ++g) acc += (g < nthr / 128) ? red_s[g][tid] : 0.f;
+    const int col = tid;
     const float val = (den > 0.f) ? acc / den : 0.f;
     const long long off = p.contiguous ? row * p.d + col : b * p.o_sb + h * p.o_sh + col;
     if (p.o_f32) reinterpret_cast<float*>(p.o)[off] = val;

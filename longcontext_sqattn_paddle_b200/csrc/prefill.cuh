@@ -38,6 +38,8 @@ struct PrefillParams {
   float* dump;  // debug builds only: S tiles of CTA 0
   int batch, hq, hkv, groups, n, kv_len;
   int mode, sink, p_fp8_mode, o_dtype, qk_bf16, same_opset, nblk;
+  int blk0;     // first 128-row block of this launch inside the whole sequence (sequence-parallel shards)
+  int n_total;  // blk0 * 128 + n: rows of the whole sequence up to the end of this shard
   int w8[kMaxHeads];
   int w4[kMaxHeads];
 };
@@ -93,7 +95,7 @@ __host__ __device__ inline int build_schedule(Seg* segs, const PrefillParams& p,
   }
   // relative windows: two 64-row blocks
   const int qs0 = blk * kBlockM, qs1 = qs0 + 64;
-  const bool has1 = qs1 < p.n;
+  const bool has1 = qs1 < p.n_total;
   for (int stage = 1; stage <= 4; ++stage) {
     int lo0, hi0, lo1 = 0, hi1 = 0;
     stage_range(stage, qs0, qs0 + 64, w8, w4, p.sink, lo0, hi0);
@@ -193,7 +195,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
-    *nseg_s = build_schedule(segs, p, blk, head);
+    *nseg_s = build_schedule(segs, p, blk + p.blk0, head);
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
     for (int i = 0; i < KS; ++i) { mbar_init(bar_k_full + 8 * i, 1); mbar_init(bar_k_empty + 8 * i, 1); }
@@ -310,7 +312,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lanes a warp may touch: 32*(warp%4) .. +31
     const int row_in_tile = quarter * 32 + lane;
     const int half_bit = (row_in_tile >= 64) ? kSegAct1 : kSegAct0;
-    const int row = blk * kBlockM + row_in_tile;
+    const int row_local = blk * kBlockM + row_in_tile;
+    const int row = row_local + p.blk0 * kBlockM;  // position in the whole sequence (causal mask)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_i = -INFINITY, l_i = 1.0f;
     bool ok = true;
@@ -386,10 +389,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     ok = __all_sync(0xffffffffu, ok);
     if (ok && nsteps > 0) {
       tc_fence_after();
-      const bool in_range = row < p.n;
+      const bool in_range = row_local < p.n;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
                       2 * (static_cast<long long>(bi) * p.o_sb + static_cast<long long>(head) * p.o_sh +
-                           static_cast<long long>(row) * p.o_sn);
+                           static_cast<long long>(row_local) * p.o_sn);
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t o[32];
@@ -408,7 +411,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         }
       }
       if (p.lse && in_range)
-        p.lse[(static_cast<long long>(bi) * p.hq + head) * p.n + row] = log2f(l_i) + m_i;
+        p.lse[(static_cast<long long>(bi) * p.hq + head) * p.n + row_local] = log2f(l_i) + m_i;
     }
     tc_fence_before();
   }

@@ -44,6 +44,9 @@ struct View4 {  // [B,H,N,D] through element strides
   long long sb, sh, sn;
   int b, h, n, d;
 };
+struct OutStrides {  // element strides of an output [B,H,N,D] (contiguous HND or token-major NHD)
+  long long sb, sh, sn;
+};
 
 // out (contiguous [B,H,N,D]) = f(in): kOp 0: x * scale rounded to the input dtype (q pre-scaling,
 // attn_triton_mix_relative.py:383-385); kOp 1: bf16 -> f16 (the kernel-side v.to(fp16), attn_triton.py:84).
@@ -108,13 +111,14 @@ __global__ void kmean_partial_kernel(View4 k, float* partial) {
     partial[(static_cast<long long>(bh) * kMeanChunks + chunk) * k.d + threadIdx.x] = s;
   }
 }
-// mean[bh][d] = (sum of the partials in chunk order) / n
+// mean[bh][d] = (sum of the partials in chunk order) / n; n == 0 stores the plain column sums (the
+// sequence-parallel path all-reduces the sums of the shards before dividing)
 __global__ void kmean_final_kernel(const float* partial, float* mean, int d, int n) {
   const int bh = blockIdx.x;
   if (threadIdx.x < d) {
     float s = 0.f;
     for (int c = 0; c < kMeanChunks; ++c) s += partial[(static_cast<long long>(bh) * kMeanChunks + c) * d + threadIdx.x];
-    mean[bh * d + threadIdx.x] = s / static_cast<float>(n);
+    mean[bh * d + threadIdx.x] = n > 0 ? s / static_cast<float>(n) : s;
   }
 }
 
@@ -163,52 +167,63 @@ __device__ __forceinline__ float fake_quant_value(float x, float absmax, int qty
 // Q: results are multiplied by 1/sqrt(D)*log2e in the input dtype.
 // One 16-lane group per row (D = 128) or one 8-lane group (D = 64); 16-byte loads and stores.
 template <bool BF16, bool kIsK>
-__global__ void quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uint8_t* out4, int qtype, int half_even,
-                                  float q_scale) {
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uint8_t* out4, OutStrides os, int qtype, int half_even,
+                  float q_scale) {
+  constexpr int kUnroll = 4;  // rows in flight per lane group: four independent 16-byte loads per thread
   const int d8 = x.d / 8;
   const int rows_per_block = blockDim.x / d8;
   const long long total_rows = static_cast<long long>(x.b) * x.h * x.n;
   const int c = threadIdx.x % d8;
   const unsigned grp_mask = (d8 == 16) ? (0xffffu << ((threadIdx.x & 16) ? 16 : 0)) : (0xffu << ((threadIdx.x & 31) / 8 * 8));
-  for (long long row = blockIdx.x * static_cast<long long>(rows_per_block) + threadIdx.x / d8;
-       row < (total_rows + rows_per_block - 1) / rows_per_block * rows_per_block;
-       row += static_cast<long long>(gridDim.x) * rows_per_block) {
-    const bool live = row < total_rows;
-    // output order [B,H,N]: consecutive rows of a block are consecutive tokens of one head
-    const long long rr = live ? row : 0;
-    const int n = static_cast<int>(rr % x.n);
-    const int h = static_cast<int>((rr / x.n) % x.h);
-    const int b = static_cast<int>(rr / (static_cast<long long>(x.n) * x.h));
-    float f[8];
-    {
-      const uint4 v = *reinterpret_cast<const uint4*>(x.ptr + 2 * (b * x.sb + h * x.sh + n * x.sn + c * 8));
-      unpack8<BF16>(v, f);
+  const long long stride = static_cast<long long>(gridDim.x) * rows_per_block * kUnroll;
+  for (long long row0 = static_cast<long long>(blockIdx.x) * rows_per_block * kUnroll + threadIdx.x / d8; row0 < total_rows;
+       row0 += stride) {
+    // output order [B,H,N]: the rows of a block are consecutive tokens of one head
+    uint4 raw[kUnroll];
+    int nn[kUnroll], hh[kUnroll], bb[kUnroll];
+    bool live[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long row = row0 + static_cast<long long>(u) * rows_per_block;
+      live[u] = row < total_rows;
+      const long long rr = live[u] ? row : 0;
+      nn[u] = static_cast<int>(rr % x.n);
+      hh[u] = static_cast<int>((rr / x.n) % x.h);
+      bb[u] = static_cast<int>(rr / (static_cast<long long>(x.n) * x.h));
+      raw[u] = *reinterpret_cast<const uint4*>(x.ptr + 2 * (bb[u] * x.sb + hh[u] * x.sh + nn[u] * x.sn + c * 8));
     }
-    if (kIsK) {
-      const float* m = mean + (static_cast<long long>(b) * x.h + h) * x.d + c * 8;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = to_f32<BF16>(from_f32<BF16>(f[i] - to_f32<BF16>(from_f32<BF16>(m[i]))));
-    }
-    float amax = 0.f;
+    for (int u = 0; u < kUnroll; ++u) {
+      float f[8];
+      unpack8<BF16>(raw[u], f);
+      if (kIsK) {
+        const float* m = mean + (static_cast<long long>(bb[u]) * x.h + hh[u]) * x.d + c * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-    for (int o = d8 / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp_mask, amax, o));
-    amax = fmaxf(amax, 1e-5f);
-    if (live) {
-      float g[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
-        if (!kIsK) g[i] *= q_scale;
+        for (int i = 0; i < 8; ++i) f[i] = to_f32<BF16>(from_f32<BF16>(f[i] - to_f32<BF16>(from_f32<BF16>(m[i]))));
       }
-      *reinterpret_cast<uint4*>(out8 + (rr * x.d + c * 8) * 2) = pack8<BF16>(g);
-      if (out4) {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      for (int o = d8 / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp_mask, amax, o));
+      amax = fmaxf(amax, 1e-5f);
+      if (live[u]) {
+        float g[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, SQATTN_QTYPE_INT, 7.0f, half_even)));
+          g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
           if (!kIsK) g[i] *= q_scale;
         }
-        *reinterpret_cast<uint4*>(out4 + (rr * x.d + c * 8) * 2) = pack8<BF16>(g);
+        const long long ooff = (bb[u] * os.sb + hh[u] * os.sh + nn[u] * os.sn + c * 8) * 2;
+        *reinterpret_cast<uint4*>(out8 + ooff) = pack8<BF16>(g);
+        if (out4) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, SQATTN_QTYPE_INT, 7.0f, half_even)));
+            if (!kIsK) g[i] *= q_scale;
+          }
+          *reinterpret_cast<uint4*>(out4 + ooff) = pack8<BF16>(g);
+        }
       }
     }
   }
@@ -217,7 +232,7 @@ __global__ void quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uin
 // "per_channel" fake-quant of V: one range per (token, channel), taken over batch and heads
 // (fake_quant.py:30-32 with a [B,H,N,D] tensor).  Output contiguous [B,H,N,D] in f16.
 template <bool BF16>
-__global__ void quant_v_kernel(View4 v, uint8_t* out, int qtype, int half_even) {
+__global__ void quant_v_kernel(View4 v, uint8_t* out, OutStrides os, int qtype, int half_even) {
   const int d8 = v.d / 8;
   const long long total = static_cast<long long>(v.n) * d8;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -241,8 +256,7 @@ __global__ void quant_v_kernel(View4 v, uint8_t* out, int qtype, int half_even) 
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           f[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax[i], qtype, 127.0f, half_even)));
-        const long long orow = (static_cast<long long>(b) * v.h + h) * v.n + n;
-        *reinterpret_cast<uint4*>(out + (orow * v.d + c * 8) * 2) = pack8<false>(f);
+        *reinterpret_cast<uint4*>(out + (b * os.sb + h * os.sh + n * os.sn + c * 8) * 2) = pack8<false>(f);
       }
   }
 }

@@ -57,7 +57,11 @@ int plan_prefill(const sqattn_prefill_args* a, PrefillPlan* pl) {
     return fail(SQATTN_ERR_INVALID_ARG, "batch/heads/lengths must be positive");
   if (a->num_q_heads % a->num_kv_heads) return fail(SQATTN_ERR_INVALID_ARG, "num_q_heads must be a multiple of num_kv_heads");
   if (a->num_q_heads > kMaxHeads) return fail(SQATTN_ERR_UNSUPPORTED, "more than %d query heads", kMaxHeads);
-  if (a->qo_len != a->kv_len) return fail(SQATTN_ERR_INVALID_ARG, "qo_len and kv_len must be equal for causal attention");
+  if (a->q_row_offset < 0 || a->q_row_offset % 128)
+    return fail(SQATTN_ERR_INVALID_ARG, "q_row_offset must be a non-negative multiple of 128, got %d", a->q_row_offset);
+  if (a->q_row_offset + a->qo_len != a->kv_len && !(a->q_row_offset + a->qo_len < a->kv_len && a->qo_len % 128 == 0))
+    return fail(SQATTN_ERR_INVALID_ARG, "qo_len and kv_len must be equal for causal attention "
+                "(a shard of query rows needs q_row_offset + qo_len <= kv_len and qo_len %% 128 == 0)");
   const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
   const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
   const size_t qbytes = static_cast<size_t>(a->batch) * a->num_q_heads * a->qo_len * a->head_dim * 2;
@@ -124,6 +128,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   p.batch = B; p.hq = Hq; p.hkv = Hkv; p.groups = Hq / Hkv; p.n = N; p.kv_len = a->kv_len;
   p.mode = a->mode; p.sink = a->sink_size; p.p_fp8_mode = a->p_fp8_mode; p.o_dtype = a->o_dtype;
   p.qk_bf16 = bf16; p.same_opset = alias; p.nblk = (N + kBlockM - 1) / kBlockM;
+  p.blk0 = a->q_row_offset / kBlockM; p.n_total = a->q_row_offset + N;
   for (int h = 0; h < Hq; ++h) {
     if (a->mode == SQATTN_MODE_RELATIVE_WINDOW) {
       p.w8[h] = relative_window(a->win8_ratios[h], a->kv_len);
@@ -196,7 +201,7 @@ int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
   long long total_tiles = 0;
   for (int b = 0; b < a->batch; ++b) {
     const int len = a->kv_lens ? a->kv_lens[b] : a->kv_len;
-    if (len <= 0) return fail(SQATTN_ERR_INVALID_ARG, "kv length of sequence %d is %d", b, len);
+    if (len < 0) return fail(SQATTN_ERR_INVALID_ARG, "kv length of sequence %d is %d", b, len);
     pl->lens[b] = len;
     total_tiles += (len + kDecTile - 1) / kDecTile;
   }
@@ -223,7 +228,8 @@ int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
 }
 
 size_t decode_ws_bytes(const sqattn_decode_args* a, const DecodePlan& pl) {
-  const size_t rows = static_cast<size_t>(pl.total_items) * a->num_q_heads;
+  // a sequence of length 0 has no work item (a rank of a sharded cache may hold none of its keys)
+  const size_t rows = static_cast<size_t>(pl.total_items > 0 ? pl.total_items : 1) * a->num_q_heads;
   return align_up(rows * a->head_dim * 4, 256) + align_up(rows * 4, 256);
 }
 
@@ -232,7 +238,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   CUtensorMap tk, tv;
   int rc;
   // the maps cover the whole cache capacity of each sequence; lengths are enforced in the kernel
-  int cap = 0;
+  int cap = 1;
   for (int b = 0; b < a->batch; ++b) cap = pl.lens[b] > cap ? pl.lens[b] : cap;
   if ((rc = make_tmap_bhnd(&tk, a->k.ptr, a->dtype, a->k.stride_b, a->k.stride_h, a->k.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "k"))) return rc;
   if ((rc = make_tmap_bhnd(&tv, a->v.ptr, a->dtype, a->v.stride_b, a->v.stride_h, a->v.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "v"))) return rc;
@@ -240,7 +246,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const uint8_t*>(a->q.ptr); p.q_sb = a->q.stride_b; p.q_sh = a->q.stride_h;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-  const size_t rows = static_cast<size_t>(pl.total_items) * a->num_q_heads;
+  const size_t rows = static_cast<size_t>(pl.total_items > 0 ? pl.total_items : 1) * a->num_q_heads;
   p.part_o = reinterpret_cast<float*>(ws);
   p.part_lse = reinterpret_cast<float*>(ws + align_up(rows * D * 4, 256));
   p.batch = a->batch; p.hq = a->num_q_heads; p.hkv = a->num_kv_heads; p.groups = a->num_q_heads / a->num_kv_heads; p.d = D;
@@ -254,9 +260,11 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
     SQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
     attr_set = true;
   }
-  dim3 grid(pl.total_items, a->num_kv_heads);
-  decode_kernel<D, BF16><<<grid, 160, L::kDynBytes, stream>>>(tk, tv, p);
-  SQ_CUDA(cudaGetLastError());
+  if (pl.total_items > 0) {
+    dim3 grid(pl.total_items, a->num_kv_heads);
+    decode_kernel<D, BF16><<<grid, 160, L::kDynBytes, stream>>>(tk, tv, p);
+    SQ_CUDA(cudaGetLastError());
+  }
 
   MergeParams m;
   memset(&m, 0, sizeof(m));
@@ -268,7 +276,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   } else {
     m.o = a->o.ptr; m.lse = a->lse; m.o_dtype = a->o_dtype; m.o_sb = a->o.stride_b; m.o_sh = a->o.stride_h;
   }
-  decode_merge_kernel<<<static_cast<unsigned>(m.rows), D, 0, stream>>>(m);
+  decode_merge_kernel<<<static_cast<unsigned>(m.rows), 128 * kMergeGroups, 0, stream>>>(m);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
@@ -326,29 +334,56 @@ int sqattn_prep_qkv(const sqattn_prep_args* a, sqattn_stream_t stream_) {
   const int B = a->batch, N = a->seq_len, D = a->head_dim, Hq = a->num_q_heads, Hkv = a->num_kv_heads;
   const bool bf16 = a->dtype == SQATTN_BF16;
   float* partial = static_cast<float*>(a->workspace);
-  float* mean = partial + static_cast<size_t>(B) * Hkv * kMeanChunks * D;
+  float* mean_ws = partial + static_cast<size_t>(B) * Hkv * kMeanChunks * D;
   View4 kq = view_of(a->q, B, Hq, N, D), kk = view_of(a->k, B, Hkv, N, D), kv = view_of(a->v, B, Hkv, N, D);
-  const int lanes = 256 / (D / 8);
-  dim3 mg(kMeanChunks, B * Hkv);
-  if (bf16) kmean_partial_kernel<true><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
-  else kmean_partial_kernel<false><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
-  kmean_final_kernel<<<B * Hkv, 128, 0, stream>>>(partial, mean, D, N);
+  const float* mean = a->k_mean;
+  if (!mean) {
+    const int lanes = 256 / (D / 8);
+    dim3 mg(kMeanChunks, B * Hkv);
+    if (bf16) kmean_partial_kernel<true><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
+    else kmean_partial_kernel<false><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
+    kmean_final_kernel<<<B * Hkv, 128, 0, stream>>>(partial, mean_ws, D, N);
+    mean = mean_ws;
+  }
   const float qs = static_cast<float>(sm_scale_log2(D));
   uint8_t* q4 = a->skip_bit4 ? nullptr : static_cast<uint8_t*>(a->q_bit4);
   uint8_t* k4 = a->skip_bit4 ? nullptr : static_cast<uint8_t*>(a->k_bit4);
+  const OutStrides qo{static_cast<long long>(Hq) * N * D, static_cast<long long>(N) * D, D};
+  const OutStrides ko = a->kv_out_nhd ? OutStrides{static_cast<long long>(N) * Hkv * D, D, static_cast<long long>(Hkv) * D}
+                                      : OutStrides{static_cast<long long>(Hkv) * N * D, static_cast<long long>(N) * D, D};
   const int rows_per_block = 256 / (D / 8);
-  const int gq = elementwise_grid((static_cast<long long>(B) * Hq * N + rows_per_block - 1) / rows_per_block, 1);
-  const int gk = elementwise_grid((static_cast<long long>(B) * Hkv * N + rows_per_block - 1) / rows_per_block, 1);
+  const int gq = elementwise_grid((static_cast<long long>(B) * Hq * N + 4 * rows_per_block - 1) / (4 * rows_per_block), 1);
+  const int gk = elementwise_grid((static_cast<long long>(B) * Hkv * N + 4 * rows_per_block - 1) / (4 * rows_per_block), 1);
   const int gv = elementwise_grid(static_cast<long long>(N) * (D / 8), 256);
   if (bf16) {
-    quant_rows_kernel<true, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, a->qk_qtype, a->round_half_even, qs);
-    quant_rows_kernel<true, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, a->qk_qtype, a->round_half_even, 1.0f);
-    quant_v_kernel<true><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), a->v_qtype, a->round_half_even);
+    quant_rows_kernel<true, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
+    quant_rows_kernel<true, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, ko, a->qk_qtype, a->round_half_even, 1.0f);
+    quant_v_kernel<true><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), ko, a->v_qtype, a->round_half_even);
   } else {
-    quant_rows_kernel<false, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, a->qk_qtype, a->round_half_even, qs);
-    quant_rows_kernel<false, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, a->qk_qtype, a->round_half_even, 1.0f);
-    quant_v_kernel<false><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), a->v_qtype, a->round_half_even);
+    quant_rows_kernel<false, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
+    quant_rows_kernel<false, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, ko, a->qk_qtype, a->round_half_even, 1.0f);
+    quant_v_kernel<false><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), ko, a->v_qtype, a->round_half_even);
   }
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_k_column_sums(const sqattn_tensor* k, int32_t batch, int32_t num_kv_heads, int32_t seq_len, int32_t head_dim,
+                         int32_t dtype, float* sums, void* workspace, size_t workspace_bytes, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!k || !k->ptr || !sums) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (head_dim != 64 && head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", head_dim);
+  if (batch <= 0 || num_kv_heads <= 0 || seq_len <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  if (!aligned16(*k)) return fail(SQATTN_ERR_INVALID_ARG, "k needs 16-byte alignment");
+  const size_t need = static_cast<size_t>(batch) * num_kv_heads * kMeanChunks * head_dim * sizeof(float);
+  if (!workspace || workspace_bytes < need) return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes required", need);
+  View4 kk = view_of(*k, batch, num_kv_heads, seq_len, head_dim);
+  const int lanes = 256 / (head_dim / 8);
+  dim3 mg(kMeanChunks, batch * num_kv_heads);
+  float* partial = static_cast<float*>(workspace);
+  if (dtype == SQATTN_BF16) kmean_partial_kernel<true><<<mg, 256, lanes * head_dim * sizeof(float), stream>>>(kk, partial);
+  else kmean_partial_kernel<false><<<mg, 256, lanes * head_dim * sizeof(float), stream>>>(kk, partial);
+  kmean_final_kernel<<<batch * num_kv_heads, 128, 0, stream>>>(partial, sums, head_dim, 0);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
@@ -386,7 +421,8 @@ int sqattn_decode_merge(const float* partial_o, const float* partial_lse, int32_
   memset(&m, 0, sizeof(m));
   m.part_o = partial_o; m.part_lse = partial_lse; m.o = o; m.lse = lse;
   m.hq = 1; m.d = head_dim; m.o_dtype = o_dtype; m.contiguous = 1; m.num_parts = num_parts; m.rows = rows;
-  decode_merge_kernel<<<static_cast<unsigned>(rows), head_dim < 128 ? 64 : 128, 0, stream>>>(m);
+  if (head_dim > 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: at most 128", head_dim);
+  decode_merge_kernel<<<static_cast<unsigned>(rows), 128 * kMergeGroups, 0, stream>>>(m);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }

@@ -54,19 +54,23 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
 
 def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0, layout: str = "HND",
             out_dtype=torch.float16, return_lse: bool = False, p_fp8_mode: int = 0, q_is_scaled: bool = False,
-            out: Optional[torch.Tensor] = None, out_layout: Optional[str] = None):
-    """sqattn_prefill.  win8/win4: per-head sequences (floats for the relative mode, ints for the absolute)."""
+            out: Optional[torch.Tensor] = None, out_layout: Optional[str] = None, kv_layout: Optional[str] = None,
+            q_row_offset: int = 0):
+    """sqattn_prefill.  win8/win4: per-head sequences (floats for the relative mode, ints for the absolute).
+    kv_layout: layout of k/v when it differs from q's; q_row_offset: first row of a query shard."""
     _require_cuda(q8, k8, q4, k4, v)
     b, hq, n, d = _shape(q8, layout)
-    _, hkv, kv_len, _ = _shape(k8, layout)
+    kv_layout = kv_layout or layout
+    _, hkv, kv_len, _ = _shape(k8, kv_layout)
     if out is None:
         out = torch.empty(q8.shape, dtype=out_dtype, device=q8.device)
         out_layout = layout
     lse = torch.empty(b, hq, n, dtype=torch.float32, device=q8.device) if return_lse else None
     a = L.PrefillArgs()
-    a.q_int8, a.k_int8 = _view(q8, layout), _view(k8, layout)
-    a.q_int4, a.k_int4 = _view(q4, layout), _view(k4, layout)
-    a.v, a.o = _view(v, layout), _view(out, out_layout)
+    a.q_int8, a.k_int8 = _view(q8, layout), _view(k8, kv_layout)
+    a.q_int4, a.k_int4 = _view(q4, layout), _view(k4, kv_layout)
+    a.v, a.o = _view(v, kv_layout), _view(out, out_layout)
+    a.q_row_offset = int(q_row_offset)
     a.lse = lse.data_ptr() if lse is not None else None
     a.batch, a.num_q_heads, a.num_kv_heads, a.qo_len, a.kv_len, a.head_dim = b, hq, hkv, n, kv_len, d
     a.qk_dtype, a.v_dtype, a.o_dtype = _dt(q8.dtype), _dt(v.dtype), _dt(out.dtype)
@@ -90,9 +94,10 @@ def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0
 
 
 def prep_qkv(query, key, value, *, qk_qtype: str = "int", v_qtype: str = "int", round_half_even: bool = False,
-             skip_bit4: bool = False):
+             skip_bit4: bool = False, k_mean: Optional[torch.Tensor] = None, kv_out_nhd: bool = False):
     """sqattn_prep_qkv: NHD inputs -> (q_bit8, q_bit4, k_bit8, k_bit4, v_bit8) contiguous HND; q pre-scaled,
-    K/V with their own Hkv heads, v_bit8 in fp16."""
+    K/V with their own Hkv heads, v_bit8 in fp16.  k_mean [B,Hkv,D] fp32 overrides the sequence mean of K;
+    kv_out_nhd writes the K/V outputs token-major [B,N,Hkv,D]."""
     _require_cuda(query, key, value)
     if qk_qtype not in L.QTYPE:
         raise ValueError(f"Invalid quantization type: {qk_qtype}")
@@ -102,10 +107,11 @@ def prep_qkv(query, key, value, *, qk_qtype: str = "int", v_qtype: str = "int", 
     hkv = key.shape[2]
     dev = query.device
     q8 = torch.empty(b, hq, n, d, dtype=query.dtype, device=dev)
-    k8 = torch.empty(b, hkv, n, d, dtype=query.dtype, device=dev)
+    kv_shape = (b, n, hkv, d) if kv_out_nhd else (b, hkv, n, d)
+    k8 = torch.empty(kv_shape, dtype=query.dtype, device=dev)
     q4 = None if skip_bit4 else torch.empty_like(q8)
     k4 = None if skip_bit4 else torch.empty_like(k8)
-    v8 = torch.empty(b, hkv, n, d, dtype=torch.float16, device=dev)
+    v8 = torch.empty(kv_shape, dtype=torch.float16, device=dev)
     a = L.PrepArgs()
     a.q, a.k, a.v = _view(query, "NHD"), _view(key, "NHD"), _view(value, "NHD")
     a.q_bit8, a.k_bit8, a.v_bit8 = q8.data_ptr(), k8.data_ptr(), v8.data_ptr()
@@ -114,11 +120,28 @@ def prep_qkv(query, key, value, *, qk_qtype: str = "int", v_qtype: str = "int", 
     a.batch, a.num_q_heads, a.num_kv_heads, a.seq_len, a.head_dim = b, hq, hkv, n, d
     a.dtype, a.qk_qtype, a.v_qtype = _dt(query.dtype), L.QTYPE[qk_qtype], L.QTYPE[v_qtype]
     a.round_half_even, a.skip_bit4 = int(round_half_even), int(skip_bit4)
+    a.kv_out_nhd = int(kv_out_nhd)
+    if k_mean is not None:
+        assert k_mean.dtype == torch.float32 and k_mean.is_contiguous() and k_mean.shape == (b, hkv, d)
+        a.k_mean = k_mean.data_ptr()
     need = L.lib.sqattn_prep_workspace_bytes(C.byref(a))
     ws = _workspace(need, dev)
     a.workspace, a.workspace_bytes = ws.data_ptr(), need
     L.check(L.lib.sqattn_prep_qkv(C.byref(a), _stream()))
     return q8, q4, k8, k4, v8
+
+
+def k_column_sums(key: torch.Tensor) -> torch.Tensor:
+    """sqattn_k_column_sums: key [B,N,Hkv,D] -> fp32 [B,Hkv,D] sums over the sequence."""
+    _require_cuda(key)
+    b, n, hkv, d = key.shape
+    sums = torch.empty(b, hkv, d, dtype=torch.float32, device=key.device)
+    nbytes = b * hkv * 64 * d * 4
+    ws = _workspace(nbytes, key.device)
+    view = _view(key, "NHD")
+    L.check(L.lib.sqattn_k_column_sums(C.byref(view), b, hkv, n, d, _dt(key.dtype), sums.data_ptr(), ws.data_ptr(),
+                                       nbytes, _stream()))
+    return sums
 
 
 def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse: bool = False, p_fp8: bool = False,

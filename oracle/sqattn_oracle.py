@@ -268,7 +268,7 @@ def windowed_prefill(q_int8, k_int8, q_int4, k_int4, v, win8, win4, sink_size: i
                      output_dtype=torch.float16, return_lse: bool = False,
                      is_P_fp8_quant: bool = False, p_fp8_mode: Optional[str] = None,
                      use_int4_operands: Optional[bool] = None,
-                     block_n: int = 64, blocks: Optional[Iterable[int]] = None):
+                     block_n: int = 64, blocks: Optional[Iterable[int]] = None, q_is_scaled: bool = False):
     """Sink + hierarchical-window causal attention.
 
     mode="relative": attn_hierarchical_relative_window
@@ -298,8 +298,9 @@ def windowed_prefill(q_int8, k_int8, q_int4, k_int4, v, win8, win4, sink_size: i
     else:
         raise ValueError(mode)
     (q_int8, k_int8, q_int4, k_int4, v), d_og = _pad_head_dim([q_int8, k_int8, q_int4, k_int4, v])
-    q8 = scale_q(_as_hnd(q_int8, tensor_layout), d_og)
-    q4 = scale_q(_as_hnd(q_int4, tensor_layout), d_og)
+    q8, q4 = _as_hnd(q_int8, tensor_layout), _as_hnd(q_int4, tensor_layout)
+    if not q_is_scaled:
+        q8, q4 = scale_q(q8, d_og), scale_q(q4, d_og)
     k8 = _as_hnd(k_int8, tensor_layout)
     k4 = _as_hnd(k_int4, tensor_layout)
     vv = _as_hnd(v, tensor_layout)

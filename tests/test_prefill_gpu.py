@@ -152,3 +152,41 @@ def test_errors(sq):
         sq.attn_causal(big, big, big)
     with pytest.raises(ValueError):
         sq.attn_causal(q, q, q, tensor_layout="XYZ")
+
+
+def test_query_shard_offsets_equal_full_call(sq):
+    """Sequence-parallel shards: calls on row ranges with q_row_offset reproduce the rows of the full call bit
+    for bit (same step lists, same tiles), with K/V token-major as the all-gather leaves them."""
+    from longcontext_sqattn_paddle_b200 import _lib as L, ops
+    n, hq, hkv, d = 1024, 4, 2, 128
+    q, k, v = so.make_inputs(9, 1, n, hq, hkv, d, torch.bfloat16)
+    q8, _, k8, _, v8 = ops.prep_qkv(q.cuda(), k.cuda(), v.cuda(), skip_bit4=True, kv_out_nhd=True)
+    assert k8.shape == (1, n, hkv, d)
+    r8, r4 = [0.2] * hq, [0.4] * hq
+    full = ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4, sink=128, kv_layout="NHD",
+                       out_dtype=torch.bfloat16, q_is_scaled=True)
+    for lo, hi in ((0, 256), (256, 1024), (512, 640)):
+        part = ops.prefill(q8[:, :, lo:hi].contiguous(), k8, q8[:, :, lo:hi].contiguous(), k8, v8,
+                           mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4, sink=128, kv_layout="NHD",
+                           out_dtype=torch.bfloat16, q_is_scaled=True, q_row_offset=lo)
+        assert torch.equal(part, full[:, :, lo:hi])
+    dense = ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_DENSE_CAUSAL, kv_layout="NHD", out_dtype=torch.bfloat16,
+                        q_is_scaled=True)
+    part = ops.prefill(q8[:, :, 384:768].contiguous(), k8, q8, k8, v8, mode=L.MODE_DENSE_CAUSAL, kv_layout="NHD",
+                       out_dtype=torch.bfloat16, q_is_scaled=True, q_row_offset=384)
+    assert torch.equal(part, dense[:, :, 384:768])
+    with pytest.raises(ValueError):
+        ops.prefill(q8[:, :, 100:228].contiguous(), k8, q8, k8, v8, mode=L.MODE_DENSE_CAUSAL, kv_layout="NHD",
+                    q_is_scaled=True, q_row_offset=100)
+
+
+def test_k_mean_override_and_column_sums():
+    from longcontext_sqattn_paddle_b200 import ops
+    q, k, v = so.make_inputs(11, 2, 777, 4, 2, 128, torch.bfloat16)
+    sums = ops.k_column_sums(k.cuda())
+    ref = k.float().sum(dim=1)
+    assert torch.allclose(sums.cpu(), ref, rtol=1e-5, atol=1e-3)
+    a = ops.prep_qkv(q.cuda(), k.cuda(), v.cuda(), skip_bit4=True)
+    b = ops.prep_qkv(q.cuda(), k.cuda(), v.cuda(), skip_bit4=True, k_mean=(sums / 777.0).contiguous())
+    assert torch.equal(a[0], b[0]) and torch.equal(a[4], b[4])
+    assert (a[2].float() != b[2].float()).float().mean().item() < 1e-3
