@@ -36,6 +36,7 @@ struct PrefillParams {
   long long o_sb, o_sh, o_sn;
   float* lse;
   float* dump;  // debug builds only: S tiles of CTA 0
+  long long* dump_t;  // debug builds only: clock64 stamps of CTA 0, [step][16]
   int batch, hq, hkv, groups, n, kv_len;
   int mode, sink, p_fp8_mode, o_dtype, qk_bf16, same_opset, nblk;
   int blk0;     // first 128-row block of this launch inside the whole sequence (sequence-parallel shards)
@@ -118,10 +119,10 @@ __host__ __device__ inline int build_schedule(Seg* segs, const PrefillParams& p,
   return n;
 }
 
-template <int D>
+template <int D, int KS_, int VS_>
 struct PrefillSmem {
-  static constexpr int kKStages = 2;
-  static constexpr int kVStages = 2;
+  static constexpr int kKStages = KS_;
+  static constexpr int kVStages = VS_;
   static constexpr int kQBytes = kBlockM * D * 2;
   static constexpr int kKBytes = kBlockN * D * 2;
   static constexpr int kVBytes = kBlockN * D * 2;
@@ -129,12 +130,12 @@ struct PrefillSmem {
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kVOff = kKOff + kKStages * kKBytes;
   static constexpr int kBarOff = kVOff + kVStages * kVBytes;
-  // barriers: q_full, q_empty, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], o_done[2]
-  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2;
+  // barriers: q_full, q_empty, k_full[KS], v_full[VS], s_full[2], p_full[2], o_done[2]
+  static constexpr int kNumBars = 2 + kKStages + kVStages + 2 + 2 + 2;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
   static constexpr int kSegOff = kMiscOff + 16;  // tmem base, abort flag, nseg
   static constexpr int kTotal = kSegOff + kMaxSegs * 12;
-  static constexpr int kDynBytes = kTotal + 1024;  // slack for 1024-byte alignment of the tiles
+  static constexpr int kDynBytes = kTotal;  // the dynamic shared memory window itself is 1024-byte aligned
 };
 
 // Walks the flattened step list.
@@ -159,27 +160,35 @@ struct StepIter {
   }
 };
 
-template <int D, bool kDump>
-__global__ void __launch_bounds__(192, 2)
+template <int D, bool kDump, int KS_, int VS_, int kMinCtas>
+__global__ void __launch_bounds__(192, kMinCtas)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PrefillParams p) {
-  using L = PrefillSmem<D>;
+  using L = PrefillSmem<D, KS_, VS_>;
   constexpr int KS = L::kKStages, VS = L::kVStages;
   constexpr uint32_t kTmemCols = 256;  // S0 [0,64) S1 [64,128) O [128,128+D)
   constexpr uint32_t kOCol = 128;
+#define SQ_STAMP(step, slot)                                                            \
+  do {                                                                                 \
+    if (kDump && blockIdx.x == 0 && p.dump_t) p.dump_t[(step) * 16 + (slot)] = clock64(); \
+  } while (0)
 
   // once a wait has given up anywhere, the remaining CTAs of the grid leave at once
   if (*reinterpret_cast<volatile int*>(&g_device_status) != 0) return;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
+  if (sbase & 1023u) {  // the 128-byte swizzle needs 1024-byte aligned tiles: refuse to run rather than compute garbage
+    if (threadIdx.x == 0) atomicCAS(&g_device_status, 0, 100);
+    return;
+  }
   const uint32_t q_s = sbase + L::kQOff, k_s = sbase + L::kKOff, v_s = sbase + L::kVOff;
   const uint32_t bars = sbase + L::kBarOff;
   const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
-  const uint32_t bar_k_full = bars + 16, bar_k_empty = bar_k_full + 8 * KS;
-  const uint32_t bar_v_full = bar_k_empty + 8 * KS, bar_v_empty = bar_v_full + 8 * VS;
-  const uint32_t bar_s_full = bar_v_empty + 8 * VS, bar_p_full = bar_s_full + 16, bar_o_done = bar_p_full + 16;
+  static_assert(KS == 2 && VS == 2, "K/V stages are tied to the two S buffers");
+  const uint32_t bar_k_full = bars + 16, bar_v_full = bar_k_full + 8 * KS;
+  const uint32_t bar_s_full = bar_v_full + 8 * VS, bar_p_full = bar_s_full + 16, bar_o_done = bar_p_full + 16;
   volatile uint32_t* tmem_base_s = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
   volatile int* nseg_s = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 8);
@@ -198,8 +207,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     *nseg_s = build_schedule(segs, p, blk + p.blk0, head);
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
-    for (int i = 0; i < KS; ++i) { mbar_init(bar_k_full + 8 * i, 1); mbar_init(bar_k_empty + 8 * i, 1); }
-    for (int i = 0; i < VS; ++i) { mbar_init(bar_v_full + 8 * i, 1); mbar_init(bar_v_empty + 8 * i, 1); }
+    for (int i = 0; i < KS; ++i) mbar_init(bar_k_full + 8 * i, 1);
+    for (int i = 0; i < VS; ++i) mbar_init(bar_v_full + 8 * i, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_s_full + 8 * i, 1); mbar_init(bar_p_full + 8 * i, 128); }
     mbar_init(bar_o_done, 1);
     mbar_init(bar_o_done + 8, 1);
@@ -220,6 +229,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // K stage (i & 1) is free again when QK^T of step i-2 has completed (s_full of that step), V stage (i & 1)
+    // when P V of step i-2 has completed (o_done): the completion barriers double as "empty" barriers, which
+    // saves the issuing threads two tcgen05.commit per step.
     if (lane == 0) {
       tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_v);
       int q_loads = 0;
@@ -236,75 +248,91 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
           for (int h = 0; h < D / 64; ++h) tma_load_4d(q_s + h * (kBlockM * 128), tq, bar_q_full, h * 64, blk * kBlockM, head, bi);
           ++q_loads;
         }
-        const int ks = i % KS, vs = i % VS;
-        ok = mbar_wait(bar_k_empty + 8 * ks, ((i / KS) & 1) ^ 1, cta_abort, 102);
+        const int st = i & 1;
+        if (i >= 2) ok = mbar_wait(bar_s_full + 8 * st, ((i - 2) >> 1) & 1, cta_abort, 102);
         if (!ok) break;
-        mbar_expect_tx(bar_k_full + 8 * ks, L::kKBytes);
+        SQ_STAMP(i, 12);
+        mbar_expect_tx(bar_k_full + 8 * st, L::kKBytes);
         const CUtensorMap* tk = int4 ? &tm_k4 : &tm_k8;
 #pragma unroll
         for (int h = 0; h < D / 64; ++h)
-          tma_load_4d(k_s + ks * L::kKBytes + h * (kBlockN * 128), tk, bar_k_full + 8 * ks, h * 64, it.key0(), kvh, bi);
-        ok = mbar_wait(bar_v_empty + 8 * vs, ((i / VS) & 1) ^ 1, cta_abort, 103);
+          tma_load_4d(k_s + st * L::kKBytes + h * (kBlockN * 128), tk, bar_k_full + 8 * st, h * 64, it.key0(), kvh, bi);
+        if (i >= 2) ok = mbar_wait(bar_o_done + 8 * st, ((i - 2) >> 1) & 1, cta_abort, 103);
         if (!ok) break;
-        mbar_expect_tx(bar_v_full + 8 * vs, L::kVBytes);
+        SQ_STAMP(i, 13);
+        mbar_expect_tx(bar_v_full + 8 * st, L::kVBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h)
-          tma_load_4d(v_s + vs * L::kVBytes + h * (kBlockN * 128), &tm_v, bar_v_full + 8 * vs, h * 64, it.key0(), kvh, bi);
+          tma_load_4d(v_s + st * L::kVBytes + h * (kBlockN * 128), &tm_v, bar_v_full + 8 * st, h * 64, it.key0(), kvh, bi);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ tcgen05 issuer
+    // Measured on B200: one tcgen05.mma costs the issuing thread ~107 cycles whatever its size (and an N = 64
+    // instruction occupies the tensor pipe as long as an N = 128 one), one tcgen05.commit ~350 cycles plus ~85
+    // for each further commit behind it.  With 12 MMAs per step this thread is the critical path of the
+    // kernel, so it does nothing else: descriptors are built once, and there is exactly one commit per batch
+    // (the completion barriers double as the producer's "stage is free" barriers).
+    // Issue order QK(i+1), PV(i): S buffer (i+1)&1 still holds P(i-1), which PV(i-1), issued earlier by this
+    // same thread, consumes first (the tensor pipe executes one thread's MMAs in issue order).
     if (lane == 0) {
       const uint32_t fmt = p.qk_bf16 ? 1u : 0u;
       const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, kBlockM, kBlockN);
       const uint32_t idesc_pv = make_idesc(0, 0, 0, 1, kBlockM, D);
+      const uint64_t q_desc = smem_desc_sw128(q_s, 16, 1024);
+      const uint64_t k_desc0 = smem_desc_sw128(k_s, 16, 1024);
+      const uint64_t v_desc0 = smem_desc_sw128(v_s, kBlockN * 128, 1024);
       bool ok = true;
       int q_uses = 0;
-      StepIter qk_it(segs, nseg), pv_it(segs, nseg);
+      StepIter qk_it(segs, nseg);
       auto issue_qk = [&](int j) {
         if (j == 0 || (qk_it.first_of_seg() && qk_it.opset_changed_before())) {
           ok = mbar_wait(bar_q_full, q_uses & 1, cta_abort, 111);
           ++q_uses;
           if (!ok) return;
         }
-        const int ks = j % KS;
-        ok = mbar_wait(bar_k_full + 8 * ks, (j / KS) & 1, cta_abort, 112);
+        const int st = j & 1;
+        SQ_STAMP(j, 0);
+        ok = mbar_wait(bar_k_full + 8 * st, (j >> 1) & 1, cta_abort, 112);
         if (!ok) return;
         tc_fence_after();
-        const uint32_t d_tmem = tmem + (j & 1) * kBlockN;
+        const uint32_t d_tmem = tmem + st * kBlockN;
+        const uint64_t k_desc = k_desc0 + static_cast<uint32_t>(st) * (L::kKBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off_q = (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32;
-          const uint32_t off_k = (kk >> 2) * (kBlockN * 128) + (kk & 3) * 32;
-          mma_ss(d_tmem, smem_desc_sw128(q_s + off_q, 16, 1024), smem_desc_sw128(k_s + ks * L::kKBytes + off_k, 16, 1024),
-                 idesc_qk, kk > 0);
+          constexpr uint32_t kHalfQ = kBlockM * 128, kHalfK = kBlockN * 128;
+          const uint32_t off_q = (kk >> 2) * kHalfQ + (kk & 3) * 32;
+          const uint32_t off_k = (kk >> 2) * kHalfK + (kk & 3) * 32;
+          // descriptors differ from the precomputed bases only in the start-address field (units of 16 bytes)
+          mma_ss(d_tmem, q_desc + (off_q >> 4), k_desc + (off_k >> 4), idesc_qk, kk > 0);
         }
-        tc_commit(bar_s_full + 8 * (j & 1));
-        tc_commit(bar_k_empty + 8 * ks);
+        tc_commit(bar_s_full + 8 * st);
+        SQ_STAMP(j, 1);
         if (qk_it.last_of_seg() && qk_it.opset_changes_after()) tc_commit(bar_q_empty);
         qk_it.next();
       };
       if (nsteps > 0) issue_qk(0);
-      for (int i = 0; ok && i < nsteps; ++i, pv_it.next()) {
+      for (int i = 0; ok && i < nsteps; ++i) {
         if (i + 1 < nsteps) { issue_qk(i + 1); if (!ok) break; }
-        ok = mbar_wait(bar_p_full + 8 * (i & 1), (i >> 1) & 1, cta_abort, 113);
+        const int st = i & 1;
+        ok = mbar_wait(bar_p_full + 8 * st, (i >> 1) & 1, cta_abort, 113);
         if (!ok) break;
-        const int vs = i % VS;
-        ok = mbar_wait(bar_v_full + 8 * vs, (i / VS) & 1, cta_abort, 114);
+        SQ_STAMP(i, 2);
+        ok = mbar_wait(bar_v_full + 8 * st, (i >> 1) & 1, cta_abort, 114);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t p_tmem = tmem + (i & 1) * kBlockN;
+        const uint32_t p_tmem = tmem + st * kBlockN;
+        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(st) * (L::kVBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // V tile: [64 keys][64 d] 128-byte rows per d-half; MN-major B operand: 64-d chunks 8 KB apart
           // (leading offset), 8-key groups 1 KB apart (stride offset); 16 keys per MMA = 2 KB.
-          mma_ts(tmem + kOCol, p_tmem + kk * 8, smem_desc_sw128(v_s + vs * L::kVBytes + kk * 2048, kBlockN * 128, 1024),
-                 idesc_pv, (i > 0 || kk > 0));
+          mma_ts(tmem + kOCol, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc_pv, (i > 0 || kk > 0));
         }
-        tc_commit(bar_v_empty + 8 * vs);
         // two alternating barriers: a waiter that is up to two steps behind the tensor pipe can still tell the
         // phases apart by parity
-        tc_commit(bar_o_done + 8 * (i & 1));
+        tc_commit(bar_o_done + 8 * st);
+        SQ_STAMP(i, 4);
       }
     }
   } else {
@@ -343,14 +371,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
 #pragma unroll
           for (int c = 0; c < 64; ++c) x[c] = x[c] + ((row >= key0 + c) ? 0.0f : -1000000.0f);
         }
-        float mx = x[0];
+        // four independent chains for the row maximum and the row sum
+        float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
 #pragma unroll
-        for (int c = 1; c < 64; ++c) mx = fmaxf(mx, x[c]);
-        const float m_new = fmaxf(m_i, mx);
+        for (int c = 4; c < 64; c += 4) {
+          mx0 = fmaxf(mx0, x[c]); mx1 = fmaxf(mx1, x[c + 1]); mx2 = fmaxf(mx2, x[c + 2]); mx3 = fmaxf(mx3, x[c + 3]);
+        }
+        const float m_new = fmaxf(m_i, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         alpha = ex2_approx(m_i - m_new);
-        float sum = 0.0f;
+        float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) { x[c] = ex2_approx(x[c] - m_new); sum += x[c]; }
+        for (int c = 0; c < 64; c += 4) {
+          x[c] = ex2_approx(x[c] - m_new); x[c + 1] = ex2_approx(x[c + 1] - m_new);
+          x[c + 2] = ex2_approx(x[c + 2] - m_new); x[c + 3] = ex2_approx(x[c + 3] - m_new);
+          s0 += x[c]; s1 += x[c + 1]; s2 += x[c + 2]; s3 += x[c + 3];
+        }
+        const float sum = (s0 + s1) + (s2 + s3);
         l_i = l_i * alpha + sum;
         m_i = m_new;
         if (flags & kSegFp8) {

@@ -173,34 +173,35 @@ quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uint8_t* out4, OutS
   constexpr int kUnroll = 4;  // rows in flight per lane group: four independent 16-byte loads per thread
   const int d8 = x.d / 8;
   const int rows_per_block = blockDim.x / d8;
-  const long long total_rows = static_cast<long long>(x.b) * x.h * x.n;
   const int c = threadIdx.x % d8;
   const unsigned grp_mask = (d8 == 16) ? (0xffffu << ((threadIdx.x & 16) ? 16 : 0)) : (0xffu << ((threadIdx.x & 31) / 8 * 8));
-  const long long stride = static_cast<long long>(gridDim.x) * rows_per_block * kUnroll;
-  for (long long row0 = static_cast<long long>(blockIdx.x) * rows_per_block * kUnroll + threadIdx.x / d8; row0 < total_rows;
-       row0 += stride) {
-    // output order [B,H,N]: the rows of a block are consecutive tokens of one head
+  // grid: x walks the tokens of one (batch, head) pair, y = b * H + h
+  const int b = static_cast<int>(blockIdx.y) / x.h, h = static_cast<int>(blockIdx.y) % x.h;
+  const uint8_t* in_base = x.ptr + 2 * (b * x.sb + h * x.sh + c * 8);
+  const long long out_base = (b * os.sb + h * os.sh + c * 8) * 2;
+  float mvals[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (kIsK) {
+    const float* m = mean + (static_cast<long long>(b) * x.h + h) * x.d + c * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mvals[i] = to_f32<BF16>(from_f32<BF16>(m[i]));
+  }
+  const int step = static_cast<int>(gridDim.x) * rows_per_block * kUnroll;
+  for (int n0 = static_cast<int>(blockIdx.x) * rows_per_block * kUnroll + threadIdx.x / d8; n0 < x.n; n0 += step) {
     uint4 raw[kUnroll];
-    int nn[kUnroll], hh[kUnroll], bb[kUnroll];
     bool live[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const long long row = row0 + static_cast<long long>(u) * rows_per_block;
-      live[u] = row < total_rows;
-      const long long rr = live[u] ? row : 0;
-      nn[u] = static_cast<int>(rr % x.n);
-      hh[u] = static_cast<int>((rr / x.n) % x.h);
-      bb[u] = static_cast<int>(rr / (static_cast<long long>(x.n) * x.h));
-      raw[u] = *reinterpret_cast<const uint4*>(x.ptr + 2 * (bb[u] * x.sb + hh[u] * x.sh + nn[u] * x.sn + c * 8));
+      const int n = n0 + u * rows_per_block;
+      live[u] = n < x.n;
+      raw[u] = *reinterpret_cast<const uint4*>(in_base + 2 * (static_cast<long long>(live[u] ? n : 0) * x.sn));
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       float f[8];
       unpack8<BF16>(raw[u], f);
       if (kIsK) {
-        const float* m = mean + (static_cast<long long>(bb[u]) * x.h + hh[u]) * x.d + c * 8;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = to_f32<BF16>(from_f32<BF16>(f[i] - to_f32<BF16>(from_f32<BF16>(m[i]))));
+        for (int i = 0; i < 8; ++i) f[i] = to_f32<BF16>(from_f32<BF16>(f[i] - mvals[i]));
       }
       float amax = 0.f;
 #pragma unroll
@@ -214,7 +215,7 @@ quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uint8_t* out4, OutS
           g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
           if (!kIsK) g[i] *= q_scale;
         }
-        const long long ooff = (bb[u] * os.sb + hh[u] * os.sh + nn[u] * os.sn + c * 8) * 2;
+        const long long ooff = out_base + static_cast<long long>(n0 + u * rows_per_block) * os.sn * 2;
         *reinterpret_cast<uint4*>(out8 + ooff) = pack8<BF16>(g);
         if (out4) {
 #pragma unroll

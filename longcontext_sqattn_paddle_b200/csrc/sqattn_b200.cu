@@ -1,6 +1,7 @@
 // C ABI of the library (declared in include/sqattn_b200.h).  Host-side argument checking, TMA descriptor
 // construction, the length-aware decode scheduler and the kernel launches.  One translation unit.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -78,7 +79,8 @@ int plan_prefill(const sqattn_prefill_args* a, PrefillPlan* pl) {
 }
 
 template <int D>
-int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStream_t stream, float* dump) {
+int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStream_t stream, float* dump,
+                   long long* dump_t = nullptr) {
   const int B = a->batch, Hq = a->num_q_heads, Hkv = a->num_kv_heads, N = a->qo_len;
   const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
   const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
@@ -124,7 +126,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   PrefillParams p;
   memset(&p, 0, sizeof(p));
   p.o = a->o.ptr; p.o_sb = a->o.stride_b; p.o_sh = a->o.stride_h; p.o_sn = a->o.stride_n;
-  p.lse = a->lse; p.dump = dump;
+  p.lse = a->lse; p.dump = dump; p.dump_t = dump_t;
   p.batch = B; p.hq = Hq; p.hkv = Hkv; p.groups = Hq / Hkv; p.n = N; p.kv_len = a->kv_len;
   p.mode = a->mode; p.sink = a->sink_size; p.p_fp8_mode = a->p_fp8_mode; p.o_dtype = a->o_dtype;
   p.qk_bf16 = bf16; p.same_opset = alias; p.nblk = (N + kBlockM - 1) / kBlockM;
@@ -138,25 +140,26 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
       p.w4[h] = a->win4_sizes[h];
     }
   }
-  using L = PrefillSmem<D>;
   const long long grid = static_cast<long long>(p.nblk) * Hq * B;
   if (grid > 0x7fffffffll) return fail(SQATTN_ERR_UNSUPPORTED, "grid too large");
-  if (dump) {
-    SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
-    prefill_kernel<D, true><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);
-  } else {
-    static bool attr_set = false;
-    if (!attr_set) {
-      SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
-      attr_set = true;
-    }
-    prefill_kernel<D, false><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);
-  }
+#define SQ_LAUNCH_PREFILL(KS, VS, MINB)                                                                                 \
+  do {                                                                                                                   \
+    using L = PrefillSmem<D, KS, VS>;                                                                                    \
+    if (dump || dump_t) {                                                                                                \
+      SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, true, KS, VS, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes)); \
+      prefill_kernel<D, true, KS, VS, MINB><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);    \
+    } else {                                                                                                             \
+      SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, false, KS, VS, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes)); \
+      prefill_kernel<D, false, KS, VS, MINB><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);   \
+    }                                                                                                                    \
+  } while (0)
+  SQ_LAUNCH_PREFILL(2, 2, 2);  // two K and two V stages (tied to the two S buffers), two CTAs per SM
+#undef SQ_LAUNCH_PREFILL
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
 
-int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump) {
+int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump, long long* dump_t = nullptr) {
   PrefillPlan pl;
   int rc = plan_prefill(a, &pl);
   if (rc) return rc;
@@ -179,7 +182,7 @@ int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump)
     return fail(SQATTN_ERR_INVALID_ARG, "o needs a 16-byte aligned pointer and strides that are multiples of 8 elements");
   if (pl.total > 0 && (!a->workspace || a->workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(a->workspace) % 1024)))
     return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (1024-byte aligned) required", pl.total);
-  return a->head_dim == 128 ? launch_prefill<128>(a, pl, stream, dump) : launch_prefill<64>(a, pl, stream, dump);
+  return a->head_dim == 128 ? launch_prefill<128>(a, pl, stream, dump, dump_t) : launch_prefill<64>(a, pl, stream, dump, dump_t);
 }
 
 // ---- decode scheduling ---------------------------------------------------------------------------------
@@ -312,6 +315,10 @@ int sqattn_debug_schedule(int mode, int n, int sink, int w8, int w4, int p_fp8_m
 int sqattn_debug_prefill_dump(const sqattn_prefill_args* args, float* dump, sqattn_stream_t stream) {
   return prefill_impl(args, reinterpret_cast<cudaStream_t>(stream), dump);
 }
+// ... and clock64 stamps of CTA 0's warps, [steps][16] (see SQ_STAMP in prefill.cuh)
+int sqattn_debug_prefill_timeline(const sqattn_prefill_args* args, float* dump, long long* stamps, sqattn_stream_t stream) {
+  return prefill_impl(args, reinterpret_cast<cudaStream_t>(stream), dump, stamps);
+}
 #endif
 
 size_t sqattn_prep_workspace_bytes(const sqattn_prep_args* a) {
@@ -352,8 +359,8 @@ int sqattn_prep_qkv(const sqattn_prep_args* a, sqattn_stream_t stream_) {
   const OutStrides ko = a->kv_out_nhd ? OutStrides{static_cast<long long>(N) * Hkv * D, D, static_cast<long long>(Hkv) * D}
                                       : OutStrides{static_cast<long long>(Hkv) * N * D, static_cast<long long>(N) * D, D};
   const int rows_per_block = 256 / (D / 8);
-  const int gq = elementwise_grid((static_cast<long long>(B) * Hq * N + 4 * rows_per_block - 1) / (4 * rows_per_block), 1);
-  const int gk = elementwise_grid((static_cast<long long>(B) * Hkv * N + 4 * rows_per_block - 1) / (4 * rows_per_block), 1);
+  const int gx = elementwise_grid((N + 4 * rows_per_block - 1) / (4 * rows_per_block), 1);
+  const dim3 gq(gx, B * Hq), gk(gx, B * Hkv);
   const int gv = elementwise_grid(static_cast<long long>(N) * (D / 8), 256);
   if (bf16) {
     quant_rows_kernel<true, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
