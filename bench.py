@@ -274,16 +274,27 @@ def run_ours(args):
 
     # ---- end to end: pinned host buffers in, host buffer out, copies inside the timed region
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-
-    def e2e_step():
-        a, b_, c = hq_.to(dev, non_blocking=True), hk_.to(dev, non_blocking=True), hv_.to(dev, non_blocking=True)
-        hout.copy_(op(a, b_, c), non_blocking=True)
+    if world == 1:
+        from longcontext_sqattn_paddle_b200.sqattn import HostPrefillPipeline
+        pipe = HostPrefillPipeline(r, r, SINK, Args(), chunk_rows=4096)
+        e2e_step = lambda: pipe(hq_, hk_, hv_, hout)
+        e2e_api = "HostPrefillPipeline (chunked H2D / kernels / D2H on three streams)"
+    else:
+        def e2e_step():
+            a, b_, c = hq_.to(dev, non_blocking=True), hk_.to(dev, non_blocking=True), hv_.to(dev, non_blocking=True)
+            hout.copy_(op(a, b_, c), non_blocking=True)
+        e2e_api = "copy in, sequence-parallel operator, copy out"
 
     for _ in range(2):
         e2e_step()
+    torch.cuda.synchronize()
+    e2e_ok = True
+    if world == 1:
+        e2e_ok = bool(torch.equal(hout, out.cpu()))
     ms_e2e = timed(e2e_step, args.steps) / args.steps
     e2e = {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": out.numel() * 2}
+           "h2d_bytes_per_step": (q.numel() + k.numel() + v.numel()) * 2, "d2h_bytes_per_step": out.numel() * 2,
+           "api": e2e_api, "matches_device_path": e2e_ok}
 
     # ---- roofline of the dominant kernel (the attention kernel alone, events on its stream)
     roof = None
@@ -299,7 +310,10 @@ def run_ours(args):
         ach = flops_total / (kms * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": "prefill_kernel<128> (relative windows)", "achieved": ach,
                 "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "peak_source": peaks["src"],
-                "ms_per_launch": kms, "traffic": None}
+                "ms_per_launch": kms,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised in
+                # profiles/prefill_kernel_relative_window_32k.md (algorithmic: Q+K+V+O = 537 MB)
+                "traffic": 494.2e6, "traffic_unit": "bytes per launch"}
         # dense causal on the same tensors: the tensor-core-bound configuration
         dense = lambda: ops.prefill(q8, k8, q8, k8, v8, mode=L.MODE_DENSE_CAUSAL, q_is_scaled=True, out=o4, out_layout="NHD")
         for _ in range(2):

@@ -111,6 +111,9 @@ typedef struct {
                                 it (sequence-parallel shards pass the mean of the whole sequence) */
   int32_t kv_out_nhd;        /* 1: k_bit8/k_bit4/v_bit8 are written token-major [B, N, Hkv, D] (so that shards
                                 all-gather into one contiguous tensor); 0: [B, Hkv, N, D] */
+  int32_t parts;             /* bit mask of the tensors to prepare: 1 = Q, 2 = K, 4 = V; 0 means all three.
+                                Pipelined callers prepare K and V once and Q chunk by chunk (the unselected
+                                pointers may be null) */
 } sqattn_prep_args;
 
 /* Replaces attention_fn's input preparation, sqattn/attn_replacer.py:334-365:

@@ -54,7 +54,7 @@ class PrepArgs(C.Structure):
         ("head_dim", C.c_int32), ("dtype", C.c_int32), ("qk_qtype", C.c_int32), ("v_qtype", C.c_int32),
         ("round_half_even", C.c_int32), ("skip_bit4", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("k_mean", C.c_void_p), ("kv_out_nhd", C.c_int32),
+        ("k_mean", C.c_void_p), ("kv_out_nhd", C.c_int32), ("parts", C.c_int32),
     ]
 
 

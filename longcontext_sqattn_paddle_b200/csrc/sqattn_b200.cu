@@ -332,9 +332,13 @@ int sqattn_prep_qkv(const sqattn_prep_args* a, sqattn_stream_t stream_) {
   if (a->head_dim != 64 && a->head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", a->head_dim);
   if (a->qk_qtype < 0 || a->qk_qtype > 2) return fail(SQATTN_ERR_INVALID_ARG, "Invalid quantization type: %d", a->qk_qtype);
   if (a->v_qtype < 0 || a->v_qtype > 2) return fail(SQATTN_ERR_INVALID_ARG, "Invalid quantization type: %d", a->v_qtype);
-  if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->q_bit8 || !a->k_bit8 || !a->v_bit8) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
-  if (!a->skip_bit4 && (!a->q_bit4 || !a->k_bit4)) return fail(SQATTN_ERR_INVALID_ARG, "q_bit4/k_bit4 missing");
-  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v)) return fail(SQATTN_ERR_INVALID_ARG, "inputs need 16-byte alignment");
+  const int parts = a->parts ? a->parts : 7;
+  const bool do_q = parts & 1, do_k = parts & 2, do_v = parts & 4;
+  if ((do_q && (!a->q.ptr || !a->q_bit8)) || (do_k && (!a->k.ptr || !a->k_bit8)) || (do_v && (!a->v.ptr || !a->v_bit8)))
+    return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
+  if (!a->skip_bit4 && ((do_q && !a->q_bit4) || (do_k && !a->k_bit4))) return fail(SQATTN_ERR_INVALID_ARG, "q_bit4/k_bit4 missing");
+  if ((do_q && !aligned16(a->q)) || (do_k && !aligned16(a->k)) || (do_v && !aligned16(a->v)))
+    return fail(SQATTN_ERR_INVALID_ARG, "inputs need 16-byte alignment");
   if (a->batch <= 0 || a->seq_len <= 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
   const size_t need = sqattn_prep_workspace_bytes(a);
   if (!a->workspace || a->workspace_bytes < need) return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes required", need);
@@ -344,7 +348,7 @@ int sqattn_prep_qkv(const sqattn_prep_args* a, sqattn_stream_t stream_) {
   float* mean_ws = partial + static_cast<size_t>(B) * Hkv * kMeanChunks * D;
   View4 kq = view_of(a->q, B, Hq, N, D), kk = view_of(a->k, B, Hkv, N, D), kv = view_of(a->v, B, Hkv, N, D);
   const float* mean = a->k_mean;
-  if (!mean) {
+  if (!mean && do_k) {
     const int lanes = 256 / (D / 8);
     dim3 mg(kMeanChunks, B * Hkv);
     if (bf16) kmean_partial_kernel<true><<<mg, 256, lanes * D * sizeof(float), stream>>>(kk, partial);
@@ -363,13 +367,13 @@ int sqattn_prep_qkv(const sqattn_prep_args* a, sqattn_stream_t stream_) {
   const dim3 gq(gx, B * Hq), gk(gx, B * Hkv);
   const int gv = elementwise_grid(static_cast<long long>(N) * (D / 8), 256);
   if (bf16) {
-    quant_rows_kernel<true, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
-    quant_rows_kernel<true, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, ko, a->qk_qtype, a->round_half_even, 1.0f);
-    quant_v_kernel<true><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), ko, a->v_qtype, a->round_half_even);
+    if (do_q) quant_rows_kernel<true, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
+    if (do_k) quant_rows_kernel<true, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, ko, a->qk_qtype, a->round_half_even, 1.0f);
+    if (do_v) quant_v_kernel<true><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), ko, a->v_qtype, a->round_half_even);
   } else {
-    quant_rows_kernel<false, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
-    quant_rows_kernel<false, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, ko, a->qk_qtype, a->round_half_even, 1.0f);
-    quant_v_kernel<false><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), ko, a->v_qtype, a->round_half_even);
+    if (do_q) quant_rows_kernel<false, false><<<gq, 256, 0, stream>>>(kq, nullptr, static_cast<uint8_t*>(a->q_bit8), q4, qo, a->qk_qtype, a->round_half_even, qs);
+    if (do_k) quant_rows_kernel<false, true><<<gk, 256, 0, stream>>>(kk, mean, static_cast<uint8_t*>(a->k_bit8), k4, ko, a->qk_qtype, a->round_half_even, 1.0f);
+    if (do_v) quant_v_kernel<false><<<gv, 256, 0, stream>>>(kv, static_cast<uint8_t*>(a->v_bit8), ko, a->v_qtype, a->round_half_even);
   }
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;

@@ -94,31 +94,46 @@ def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0
 
 
 def prep_qkv(query, key, value, *, qk_qtype: str = "int", v_qtype: str = "int", round_half_even: bool = False,
-             skip_bit4: bool = False, k_mean: Optional[torch.Tensor] = None, kv_out_nhd: bool = False):
+             skip_bit4: bool = False, k_mean: Optional[torch.Tensor] = None, kv_out_nhd: bool = False,
+             out: Optional[dict] = None):
     """sqattn_prep_qkv: NHD inputs -> (q_bit8, q_bit4, k_bit8, k_bit4, v_bit8) contiguous HND; q pre-scaled,
     K/V with their own Hkv heads, v_bit8 in fp16.  k_mean [B,Hkv,D] fp32 overrides the sequence mean of K;
-    kv_out_nhd writes the K/V outputs token-major [B,N,Hkv,D]."""
-    _require_cuda(query, key, value)
+    kv_out_nhd writes the K/V outputs token-major [B,N,Hkv,D].  Any of query/key/value may be None: only the
+    tensors given are prepared (their outputs are returned, the others are None).  ``out`` may hold
+    preallocated outputs under the keys q8, q4, k8, k4, v8."""
+    given = [t for t in (query, key, value) if t is not None]
+    _require_cuda(*given)
     if qk_qtype not in L.QTYPE:
         raise ValueError(f"Invalid quantization type: {qk_qtype}")
     if v_qtype not in L.QTYPE:
         raise ValueError(f"Invalid quantization type: {v_qtype}")
-    b, n, hq, d = query.shape
-    hkv = key.shape[2]
-    dev = query.device
-    q8 = torch.empty(b, hq, n, d, dtype=query.dtype, device=dev)
-    kv_shape = (b, n, hkv, d) if kv_out_nhd else (b, hkv, n, d)
-    k8 = torch.empty(kv_shape, dtype=query.dtype, device=dev)
-    q4 = None if skip_bit4 else torch.empty_like(q8)
-    k4 = None if skip_bit4 else torch.empty_like(k8)
-    v8 = torch.empty(kv_shape, dtype=torch.float16, device=dev)
+    ref = given[0]
+    b, n, _, d = ref.shape
+    dev, dt = ref.device, ref.dtype
+    out = out or {}
     a = L.PrepArgs()
-    a.q, a.k, a.v = _view(query, "NHD"), _view(key, "NHD"), _view(value, "NHD")
-    a.q_bit8, a.k_bit8, a.v_bit8 = q8.data_ptr(), k8.data_ptr(), v8.data_ptr()
-    a.q_bit4 = None if q4 is None else q4.data_ptr()
-    a.k_bit4 = None if k4 is None else k4.data_ptr()
+    q8 = q4 = k8 = k4 = v8 = None
+    hq = hkv = 1
+    if query is not None:
+        hq = query.shape[2]
+        q8 = out.get("q8") if out.get("q8") is not None else torch.empty(b, hq, n, d, dtype=dt, device=dev)
+        q4 = None if skip_bit4 else (out.get("q4") if out.get("q4") is not None else torch.empty_like(q8))
+        a.q, a.q_bit8, a.q_bit4 = _view(query, "NHD"), q8.data_ptr(), (None if q4 is None else q4.data_ptr())
+        a.parts |= 1
+    if key is not None or value is not None:
+        hkv = (key if key is not None else value).shape[2]
+    kv_shape = (b, n, hkv, d) if kv_out_nhd else (b, hkv, n, d)
+    if key is not None:
+        k8 = out.get("k8") if out.get("k8") is not None else torch.empty(kv_shape, dtype=dt, device=dev)
+        k4 = None if skip_bit4 else (out.get("k4") if out.get("k4") is not None else torch.empty_like(k8))
+        a.k, a.k_bit8, a.k_bit4 = _view(key, "NHD"), k8.data_ptr(), (None if k4 is None else k4.data_ptr())
+        a.parts |= 2
+    if value is not None:
+        v8 = out.get("v8") if out.get("v8") is not None else torch.empty(kv_shape, dtype=torch.float16, device=dev)
+        a.v, a.v_bit8 = _view(value, "NHD"), v8.data_ptr()
+        a.parts |= 4
     a.batch, a.num_q_heads, a.num_kv_heads, a.seq_len, a.head_dim = b, hq, hkv, n, d
-    a.dtype, a.qk_qtype, a.v_qtype = _dt(query.dtype), L.QTYPE[qk_qtype], L.QTYPE[v_qtype]
+    a.dtype, a.qk_qtype, a.v_qtype = _dt(dt), L.QTYPE[qk_qtype], L.QTYPE[v_qtype]
     a.round_half_even, a.skip_bit4 = int(round_half_even), int(skip_bit4)
     a.kv_out_nhd = int(kv_out_nhd)
     if k_mean is not None:

@@ -84,3 +84,104 @@ def mp_triton_wrapper(layer_idx, bit8_window_sizes=0, bit4_window_sizes=0, sink_
         return out
 
     return attention_fn
+
+
+class HostPrefillPipeline:
+    """The same operator for callers whose activations live in PINNED HOST memory (layer-wise offloading runtimes
+    such as the reference's, which keeps the KV cache on the host during prefill, cache_hub/flash_attn_cache.py):
+    ``pipe(q_host, k_host, v_host, out_host)`` with q [1,N,Hq,D], k/v [1,N,Hkv,D] -> out [1,N,Hq*D].
+
+    K and V are uploaded and prepared once; Q is uploaded, prepared and attended in chunks of ``chunk_rows``
+    query rows (sqattn_prefill with q_row_offset) while the previous chunk's output travels back, so the H2D
+    copy, the kernels and the D2H copy overlap on three streams.  Results are identical to the one-shot
+    operator: chunks only partition the query rows."""
+
+    def __init__(self, bit8_window_sizes=0, bit4_window_sizes=0, sink_window_size=0, args=None, chunk_rows=4096,
+                 p_fp8_mode="off", device=None):
+        self.bit8, self.bit4 = _normalise_windows(bit8_window_sizes, bit4_window_sizes)
+        self.sink, self.args, self.chunk = sink_window_size, args, int(chunk_rows)
+        if self.chunk % 128:
+            raise ValueError("chunk_rows must be a multiple of 128")
+        self.fp8 = {"off": L.P_FP8_OFF, "all": L.P_FP8_ALL, "stage2": L.P_FP8_STAGE2}[p_fp8_mode]
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self._shape, self._buf = None, None
+
+    def _buffers(self, n, hq, hkv, d, dtype):
+        key = (n, hq, hkv, d, dtype)
+        if self._shape != key:
+            dev, c = self.device, min(self.chunk, n)
+            self._buf = {
+                "k": torch.empty(1, n, hkv, d, dtype=dtype, device=dev), "v": torch.empty(1, n, hkv, d, dtype=dtype, device=dev),
+                "k8": torch.empty(1, hkv, n, d, dtype=dtype, device=dev), "v8": torch.empty(1, hkv, n, d, dtype=torch.float16, device=dev),
+                "q": [torch.empty(1, c, hq, d, dtype=dtype, device=dev) for _ in range(2)],
+                "q8": [torch.empty(1, hq, c, d, dtype=dtype, device=dev) for _ in range(2)],
+                "o": [torch.empty(1, c, hq * d, dtype=torch.bfloat16, device=dev) for _ in range(2)],
+            }
+            self._shape = key
+        return self._buf
+
+    def __call__(self, q_host, k_host, v_host, out_host=None):
+        a = self.args
+        if not a.use_relative_distance:
+            raise ValueError("the host pipeline is implemented for relative windows")
+        for t in (q_host, k_host, v_host):
+            if t.is_cuda or not t.is_pinned():
+                raise ValueError("q, k and v must be pinned host tensors")
+        b, n, hq, d = q_host.shape
+        hkv = k_host.shape[2]
+        if b != 1:
+            raise ValueError("the host pipeline takes one sequence (batch 1)")
+        if out_host is None:
+            out_host = torch.empty(1, n, hq * d, dtype=torch.bfloat16).pin_memory()
+        buf = self._buffers(n, hq, hkv, d, q_host.dtype)
+        cur = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+
+        def per_head(w):
+            return [float(w)] * hq if isinstance(w, (int, float)) else [float(x) for x in w]
+
+        r8, r4 = per_head(self.bit8), per_head(self.bit4)
+        with torch.cuda.stream(self.s_in):
+            buf["k"].copy_(k_host, non_blocking=True)
+            buf["v"].copy_(v_host, non_blocking=True)
+            ev_kv = torch.cuda.Event()
+            ev_kv.record(self.s_in)
+        cur.wait_event(ev_kv)
+        ops.prep_qkv(None, buf["k"], buf["v"], qk_qtype=a.qk_qtype, v_qtype=a.v_qtype, skip_bit4=True,
+                     out={"k8": buf["k8"], "v8": buf["v8"]})
+        q_free = [None, None]   # compute has finished reading q buffer s
+        o_free = [None, None]   # the D2H copy has finished reading output buffer s
+        for ci, r0 in enumerate(range(0, n, self.chunk)):
+            r1 = min(n, r0 + self.chunk)
+            rows, s = r1 - r0, ci & 1
+            with torch.cuda.stream(self.s_in):
+                if q_free[s] is not None:
+                    self.s_in.wait_event(q_free[s])
+                buf["q"][s][:, :rows].copy_(q_host[:, r0:r1], non_blocking=True)
+                ev_q = torch.cuda.Event()
+                ev_q.record(self.s_in)
+            cur.wait_event(ev_q)
+            if o_free[s] is not None:
+                cur.wait_event(o_free[s])
+            q8 = buf["q8"][s][:, :, :rows]
+            if rows != buf["q8"][s].shape[2]:
+                q8 = torch.empty(1, hq, rows, d, dtype=q_host.dtype, device=self.device)
+            ops.prep_qkv(buf["q"][s][:, :rows], None, None, qk_qtype=a.qk_qtype, v_qtype=a.v_qtype, skip_bit4=True,
+                         out={"q8": q8})
+            o = buf["o"][s][:, :rows]
+            ops.prefill(q8, buf["k8"], q8, buf["k8"], buf["v8"], mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4,
+                        sink=self.sink, layout="HND", p_fp8_mode=self.fp8, q_is_scaled=True,
+                        out=o.view(1, rows, hq, d), out_layout="NHD", q_row_offset=r0)
+            ev_c = torch.cuda.Event()
+            ev_c.record(cur)
+            q_free[s] = ev_c
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_c)
+                out_host[:, r0:r1].copy_(o, non_blocking=True)
+                ev_o = torch.cuda.Event()
+                ev_o.record(self.s_out)
+            o_free[s] = ev_o
+        cur.wait_stream(self.s_out)
+        return out_host

@@ -75,3 +75,26 @@ def test_operator_boundary():
     out = model.layers[2].prefill_attention(q.cuda(), k.cuda(), v.cuda(), None)
     ref = so.attention_fn(q, k, v, hq // hkv, [128] * hq, [256] * hq, 256, use_relative_distance=False)
     assert (out.float().cpu() - ref.float()).abs().max().item() < 2e-2
+
+
+def test_host_pipeline_matches_operator():
+    """Pinned host tensors in, pinned host tensor out, chunked over query rows: bit-identical to the one-shot
+    operator (the last chunk is ragged)."""
+    from longcontext_sqattn_paddle_b200.sqattn import HostPrefillPipeline, mp_triton_wrapper
+    hq, hkv, n, d = 8, 2, 1280 + 384, 128
+    q, k, v = so.make_inputs(13, 1, n, hq, hkv, d, torch.bfloat16)
+
+    class Layer:
+        num_key_value_groups = hq // hkv
+
+    class Args:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", True
+
+    ref = mp_triton_wrapper(0, [0.2] * hq, [0.4] * hq, 256, Args())(Layer(), q.cuda(), k.cuda(), v.cuda(), None)
+    pipe = HostPrefillPipeline([0.2] * hq, [0.4] * hq, 256, Args(), chunk_rows=512)
+    for _ in range(2):   # buffers are reused across calls
+        out = pipe(q.pin_memory(), k.pin_memory(), v.pin_memory())
+        torch.cuda.synchronize()
+        assert out.is_pinned() and torch.equal(out, ref.cpu())
+    with pytest.raises(ValueError):
+        pipe(q, k, v)   # pageable host memory
