@@ -206,6 +206,23 @@ int sqattn_kmeans_index_add(const void* value, int32_t dtype, const int32_t* idx
 /* max over counts[G*K] into *out_max (device int32, zeroed by the caller): data_cnt.max(), kmeans.py:195 */
 int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, sqattn_stream_t stream);
 
+/* ---- clustered retrieval (no counterpart in the reference's code; its logs print n_clusters / nprobe / budget
+ * arguments of a retrieval step that was not shipped, logs/SQAttn_131072_qwen2.5-7b.log:11,46) ---- */
+
+/* Per KV group g: score_c = <mean over the group's query heads, centroid c> (fp64), clusters taken in descending
+ * score (lowest index on ties, empty clusters skipped) until at least `budget` tokens are covered; the tokens of
+ * the selected clusters are written to out_idx[g, :out_count[g]] in ascending order (at most `cap`).
+ * q [G, heads_per_group, D], centroids [G, K, D], cluster_size [G, K], clusters [G, K, max_cluster_size] as
+ * produced by sqattn_kmeans_*; K <= 4096, num_tokens <= 262144. */
+int sqattn_retrieve_select(const void* q, const void* centroids, int32_t dtype, const int32_t* cluster_size,
+                           const int32_t* clusters, int32_t groups_kv, int32_t heads_per_group, int32_t num_clusters,
+                           int32_t head_dim, int32_t max_cluster_size, int32_t num_tokens, int32_t budget,
+                           int32_t* out_idx, int32_t* out_count, int32_t cap, sqattn_stream_t stream);
+/* dst[g, j, :] = src[g, idx[g, j], :] for j < count[g] (16-bit rows of head_dim elements; strides in elements) */
+int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_row_stride, const int32_t* idx,
+                       const int32_t* count, int32_t groups, int32_t cap, int32_t head_dim, void* dst,
+                       sqattn_stream_t stream);
+
 /* ---- KV cache block mover (cache_hub/flash_attn_cache.py:7-19, 143-151, 200-227) ---------- */
 
 /* Gather rows [row0, row0+rows) of a [*, row_elems] 16-bit matrix that lives in (pinned) host or device

@@ -1,0 +1,147 @@
+// Centroid-scored retrieval for clustered decode (the step the reference's logs hint at but its code lacks):
+// score every cluster by <mean query of the KV group, centroid>, take clusters in descending score until a
+// token budget is covered, emit the selected token indices in ascending order, gather their K/V rows.
+// Scores are fp64 (exact products of 16-bit centroids and an fp32 mean, index-order sum), the selection is a
+// block-level argmax with lowest-index tie-break, so the selected indices are bit-exact and timing-independent.
+#pragma once
+#include "prep.cuh"
+
+namespace sq {
+
+constexpr int kRetMaxClusters = 4096;
+constexpr int kRetMaxTokens = 262144;
+
+struct RetrieveParams {
+  const uint8_t* q;         // [G, groups, D] 16-bit
+  const uint8_t* cent;      // [G, K, D] 16-bit
+  const int* cluster_size;  // [G, K]
+  const int* clusters;      // [G, K, max_cluster_size]
+  int* out_idx;             // [G, cap]
+  int* out_count;           // [G]
+  int groups, num_clusters, d, max_cluster_size, num_tokens, budget, cap;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(1024) retrieve_select_kernel(const __grid_constant__ RetrieveParams p) {
+  extern __shared__ __align__(16) uint8_t rs[];
+  double* scores = reinterpret_cast<double*>(rs);                                   // [K]
+  uint32_t* bitmap = reinterpret_cast<uint32_t*>(rs + sizeof(double) * p.num_clusters);  // [ceil(T/32)]
+  __shared__ float q_mean[128];
+  __shared__ double red_v[32];
+  __shared__ int red_i[32];
+  __shared__ int sel_list[kRetMaxClusters];
+  __shared__ int n_sel, total_tok, warp_sums[32];
+  const int g = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = p.num_clusters, D = p.d;
+  const uint16_t* q = reinterpret_cast<const uint16_t*>(p.q) + static_cast<long long>(g) * p.groups * D;
+  const uint16_t* cent = reinterpret_cast<const uint16_t*>(p.cent) + static_cast<long long>(g) * K * D;
+  const int* csize = p.cluster_size + static_cast<long long>(g) * K;
+  const int* cl = p.clusters + static_cast<long long>(g) * K * p.max_cluster_size;
+  const int words = (p.num_tokens + 31) / 32;
+
+  if (tid < D) {  // mean query of the group: fp32, heads added in order
+    float s = 0.f;
+    for (int h = 0; h < p.groups; ++h) s += to_f32<BF16>(q[h * D + tid]);
+    q_mean[tid] = s / static_cast<float>(p.groups);
+  }
+  for (int w = tid; w < words; w += blockDim.x) bitmap[w] = 0u;
+  if (tid == 0) { n_sel = 0; total_tok = 0; }
+  __syncthreads();
+  for (int c = tid; c < K; c += blockDim.x) {
+    double s = 0.0;
+    for (int d = 0; d < D; ++d) s += static_cast<double>(to_f32<BF16>(cent[static_cast<long long>(c) * D + d])) * static_cast<double>(q_mean[d]);
+    scores[c] = (csize[c] > 0) ? s : -1.0 / 0.0;  // empty clusters are never taken
+  }
+  __syncthreads();
+  // greedy selection: best remaining cluster until the budget is covered
+  for (int iter = 0; iter < K; ++iter) {
+    if (total_tok >= p.budget) break;
+    double bv = -1.0 / 0.0;
+    int bi = 0x7fffffff;
+    for (int c = tid; c < K; c += blockDim.x) {
+      const double v = scores[c];
+      if (v > bv || (v == bv && c < bi && v != -1.0 / 0.0)) { bv = v; bi = c; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+      double v = red_v[0];
+      int i = red_i[0];
+      for (int w = 1; w < (blockDim.x >> 5); ++w)
+        if (red_v[w] > v || (red_v[w] == v && red_i[w] < i)) { v = red_v[w]; i = red_i[w]; }
+      if (v == -1.0 / 0.0 || i == 0x7fffffff) {
+        total_tok = 0x7fffffff;  // nothing left
+      } else {
+        sel_list[n_sel++] = i;
+        total_tok += csize[i];
+        scores[i] = -1.0 / 0.0;
+      }
+    }
+    __syncthreads();
+  }
+  // members of the selected clusters -> bitmap over token positions
+  const int ns = n_sel;
+  for (int s = warp; s < ns; s += (blockDim.x >> 5)) {
+    const int c = sel_list[s];
+    const int n = min(csize[c], p.max_cluster_size);
+    for (int j = lane; j < n; j += 32) {
+      const int tok = cl[static_cast<long long>(c) * p.max_cluster_size + j];
+      atomicOr(&bitmap[tok >> 5], 1u << (tok & 31));
+    }
+  }
+  __syncthreads();
+  // ordered compaction: each thread owns a contiguous run of bitmap words
+  const int per = (words + blockDim.x - 1) / blockDim.x;
+  const int w0 = min(words, tid * per), w1 = min(words, w0 + per);
+  int cnt = 0;
+  for (int w = w0; w < w1; ++w) cnt += __popc(bitmap[w]);
+  int incl = cnt;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int v = warp_sums[lane];
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    warp_sums[lane] = v;
+  }
+  __syncthreads();
+  int pos = incl - cnt + (warp > 0 ? warp_sums[warp - 1] : 0);
+  int* out = p.out_idx + static_cast<long long>(g) * p.cap;
+  for (int w = w0; w < w1; ++w) {
+    uint32_t bits = bitmap[w];
+    while (bits) {
+      const int b = __ffs(bits) - 1;
+      bits &= bits - 1;
+      if (pos < p.cap) out[pos] = w * 32 + b;
+      ++pos;
+    }
+  }
+  if (tid == blockDim.x - 1) p.out_count[g] = min(pos, p.cap);
+}
+
+// dst[g, j, :] = src[g, idx[g, j], :] for j < count[g]  (16-byte chunks; src rows `src_row_stride` elements apart)
+__global__ void gather_rows_kernel(const uint8_t* src, long long src_group_stride, long long src_row_stride, const int* idx,
+                                   const int* count, int cap, int d, uint8_t* dst) {
+  const int g = blockIdx.y, d8 = d / 8;
+  const int n = count[g];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < static_cast<long long>(n) * d8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i / d8), c = static_cast<int>(i % d8);
+    const int tok = idx[static_cast<long long>(g) * cap + j];
+    const uint4 v = *reinterpret_cast<const uint4*>(src + 2 * (g * src_group_stride + tok * src_row_stride + c * 8));
+    *reinterpret_cast<uint4*>(dst + 2 * ((static_cast<long long>(g) * cap + j) * d + c * 8)) = v;
+  }
+}
+
+}  // namespace sq

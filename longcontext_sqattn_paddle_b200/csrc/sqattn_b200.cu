@@ -9,6 +9,7 @@
 #include "kmeans.cuh"
 #include "prefill.cuh"
 #include "prep.cuh"
+#include "retrieval.cuh"
 
 using namespace sq;
 
@@ -569,6 +570,48 @@ int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!counts || !out_max || n <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad arguments");
   max_int_kernel<<<elementwise_grid(n, 256), 256, 0, stream>>>(counts, n, out_max);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+// ---- retrieval -----------------------------------------------------------------------------------------
+int sqattn_retrieve_select(const void* q, const void* centroids, int32_t dtype, const int32_t* cluster_size,
+                           const int32_t* clusters, int32_t groups_kv, int32_t heads_per_group, int32_t num_clusters,
+                           int32_t head_dim, int32_t max_cluster_size, int32_t num_tokens, int32_t budget,
+                           int32_t* out_idx, int32_t* out_count, int32_t cap, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!q || !centroids || !cluster_size || !clusters || !out_idx || !out_count) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (head_dim > 128 || head_dim % 8) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: at most 128, multiple of 8", head_dim);
+  if (num_clusters <= 0 || num_clusters > kRetMaxClusters) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d clusters supported", kRetMaxClusters);
+  if (num_tokens <= 0 || num_tokens > kRetMaxTokens) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d tokens supported", kRetMaxTokens);
+  if (groups_kv <= 0 || heads_per_group <= 0 || budget <= 0 || cap <= 0 || max_cluster_size <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  RetrieveParams p;
+  p.q = static_cast<const uint8_t*>(q); p.cent = static_cast<const uint8_t*>(centroids);
+  p.cluster_size = cluster_size; p.clusters = clusters; p.out_idx = out_idx; p.out_count = out_count;
+  p.groups = heads_per_group; p.num_clusters = num_clusters; p.d = head_dim; p.max_cluster_size = max_cluster_size;
+  p.num_tokens = num_tokens; p.budget = budget; p.cap = cap;
+  const size_t smem = sizeof(double) * num_clusters + sizeof(uint32_t) * ((num_tokens + 31) / 32);
+  if (dtype == SQATTN_BF16) {
+    SQ_CUDA(cudaFuncSetAttribute(retrieve_select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    retrieve_select_kernel<true><<<groups_kv, 1024, smem, stream>>>(p);
+  } else {
+    SQ_CUDA(cudaFuncSetAttribute(retrieve_select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    retrieve_select_kernel<false><<<groups_kv, 1024, smem, stream>>>(p);
+  }
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_row_stride, const int32_t* idx,
+                       const int32_t* count, int32_t groups, int32_t cap, int32_t head_dim, void* dst,
+                       sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!src || !idx || !count || !dst) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (groups <= 0 || cap <= 0 || head_dim <= 0 || head_dim % 8 || src_row_stride % 8 || src_group_stride % 8)
+    return fail(SQATTN_ERR_INVALID_ARG, "bad sizes or strides (multiples of 8 elements)");
+  dim3 grid(elementwise_grid(static_cast<long long>(cap) * (head_dim / 8), 256) , groups);
+  gather_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(src), src_group_stride, src_row_stride, idx, count, cap,
+                                               head_dim, static_cast<uint8_t*>(dst));
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
