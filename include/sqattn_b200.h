@@ -223,6 +223,19 @@ int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_ro
                        const int32_t* count, int32_t groups, int32_t cap, int32_t head_dim, void* dst,
                        sqattn_stream_t stream);
 
+/* ---- window calibration (sqattn/window_search.py) ------------------------------------------------------ */
+
+/* Distance-weighted attention-energy histogram per query head, accumulated into hist [Hq, num_bins] (fp64, not
+ * cleared: samples add up like the reference's `histograms[head] += hist`, window_search.py:207-208).
+ * relative = 1: compute_relative_attention_histogram_gpu_with_sink (244-283); relative = 0:
+ * compute_absolute_attention_histogram_gpu_with_sink (286-321; sink = 0 gives compute_attention_histogram_gpu,
+ * 20-48), num_bins = max_len.  The softmax map A = softmax(q k^T / sqrt(D)) with a causal mask
+ * (cal_attn_weight, sqattn/attn_replacer.py:253-278) is evaluated blockwise and never stored.
+ * q [Hq, N, D], k [Hkv, N, D] contiguous 16-bit. */
+int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t num_q_heads, int32_t num_kv_heads,
+                            int32_t seq_len, int32_t head_dim, int32_t relative, int32_t num_bins, int32_t sink,
+                            double* hist, sqattn_stream_t stream);
+
 /* ---- KV cache block mover (cache_hub/flash_attn_cache.py:7-19, 143-151, 200-227) ---------- */
 
 /* Gather rows [row0, row0+rows) of a [*, row_elems] 16-bit matrix that lives in (pinned) host or device

@@ -97,6 +97,8 @@ SYMBOLS = [
                                          C.c_int32, C.c_void_p]),
     ("sqattn_gather_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                      C.c_int32, C.c_void_p, C.c_void_p]),
+    ("sqattn_window_histogram", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     ("sqattn_cache_copy_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
                                          C.c_void_p]),
     ("sqattn_check_device_status", C.c_int, [C.c_void_p]),

@@ -10,6 +10,7 @@
 #include "prefill.cuh"
 #include "prep.cuh"
 #include "retrieval.cuh"
+#include "window_search.cuh"
 
 using namespace sq;
 
@@ -612,6 +613,33 @@ int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_ro
   dim3 grid(elementwise_grid(static_cast<long long>(cap) * (head_dim / 8), 256) , groups);
   gather_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(src), src_group_stride, src_row_stride, idx, count, cap,
                                                head_dim, static_cast<uint8_t*>(dst));
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+// ---- window calibration ----------------------------------------------------------------------------------
+int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t num_q_heads, int32_t num_kv_heads,
+                            int32_t seq_len, int32_t head_dim, int32_t relative, int32_t num_bins, int32_t sink,
+                            double* hist, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!q || !k || !hist) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (head_dim % 8 || head_dim <= 0 || head_dim > 256) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d", head_dim);
+  if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || seq_len <= 0 || num_bins <= 0 || sink < 0)
+    return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  const size_t smem = (8 * static_cast<size_t>(head_dim) + num_bins) * sizeof(float);
+  if (smem > 200 * 1024) return fail(SQATTN_ERR_UNSUPPORTED, "too many bins (%d)", num_bins);
+  WindowHistParams p;
+  p.q = static_cast<const uint8_t*>(q); p.k = static_cast<const uint8_t*>(k); p.hist = hist;
+  p.hq = num_q_heads; p.groups = num_q_heads / num_kv_heads; p.n = seq_len; p.d = head_dim; p.nbins = num_bins;
+  p.sink = sink; p.relative = relative; p.scale = static_cast<float>(1.0 / sqrt(static_cast<double>(head_dim)));
+  dim3 grid(elementwise_grid((seq_len + 7) / 8, 1), num_q_heads);
+  if (dtype == SQATTN_BF16) {
+    SQ_CUDA(cudaFuncSetAttribute(window_hist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    window_hist_kernel<true><<<grid, 256, smem, stream>>>(p);
+  } else {
+    SQ_CUDA(cudaFuncSetAttribute(window_hist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    window_hist_kernel<false><<<grid, 256, smem, stream>>>(p);
+  }
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
