@@ -371,21 +371,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
 #pragma unroll
           for (int c = 0; c < 64; ++c) x[c] = x[c] + ((row >= key0 + c) ? 0.0f : -1000000.0f);
         }
-        // four independent chains for the row maximum and the row sum
+        // four independent chains for the row maximum (three-input max) and the row sum (packed fp32 pairs)
         float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
 #pragma unroll
-        for (int c = 4; c < 64; c += 4) {
-          mx0 = fmaxf(mx0, x[c]); mx1 = fmaxf(mx1, x[c + 1]); mx2 = fmaxf(mx2, x[c + 2]); mx3 = fmaxf(mx3, x[c + 3]);
+        for (int c = 4; c < 60; c += 8) {
+          mx0 = max3(mx0, x[c], x[c + 1]); mx1 = max3(mx1, x[c + 2], x[c + 3]);
+          mx2 = max3(mx2, x[c + 4], x[c + 5]); mx3 = max3(mx3, x[c + 6], x[c + 7]);
         }
-        const float m_new = fmaxf(m_i, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+        mx0 = max3(mx0, x[60], x[61]); mx1 = max3(mx1, x[62], x[63]);
+        const float m_new = fmaxf(max3(m_i, mx0, mx1), fmaxf(mx2, mx3));
         alpha = ex2_approx(m_i - m_new);
-        float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        const uint64_t m2 = f32x2_pack(m_new, m_new);
+        uint64_t sa = f32x2_pack(0.0f, 0.0f), sb = sa;
 #pragma unroll
         for (int c = 0; c < 64; c += 4) {
-          x[c] = ex2_approx(x[c] - m_new); x[c + 1] = ex2_approx(x[c + 1] - m_new);
-          x[c + 2] = ex2_approx(x[c + 2] - m_new); x[c + 3] = ex2_approx(x[c + 3] - m_new);
-          s0 += x[c]; s1 += x[c + 1]; s2 += x[c + 2]; s3 += x[c + 3];
+          float a0, a1, b0, b1;
+          f32x2_unpack(f32x2_sub(f32x2_pack(x[c], x[c + 1]), m2), a0, a1);
+          f32x2_unpack(f32x2_sub(f32x2_pack(x[c + 2], x[c + 3]), m2), b0, b1);
+          x[c] = ex2_approx(a0); x[c + 1] = ex2_approx(a1); x[c + 2] = ex2_approx(b0); x[c + 3] = ex2_approx(b1);
+          sa = f32x2_add(sa, f32x2_pack(x[c], x[c + 1]));
+          sb = f32x2_add(sb, f32x2_pack(x[c + 2], x[c + 3]));
         }
+        float s0, s1, s2, s3;
+        f32x2_unpack(sa, s0, s1);
+        f32x2_unpack(sb, s2, s3);
         const float sum = (s0 + s1) + (s2 + s3);
         l_i = l_i * alpha + sum;
         m_i = m_new;
@@ -412,8 +421,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
           uint32_t o[32];
           tmem_ld32(tmem + lane_addr + kOCol + c0, o);
           tmem_wait_ld();
+          const uint64_t al2 = f32x2_pack(alpha, alpha);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+          for (int c = 0; c < 32; c += 2) {
+            float a, b;
+            f32x2_unpack(f32x2_mul(f32x2_pack(__uint_as_float(o[c]), __uint_as_float(o[c + 1])), al2), a, b);
+            o[c] = __float_as_uint(a); o[c + 1] = __float_as_uint(b);
+          }
           tmem_st32(tmem + lane_addr + kOCol + c0, o);
         }
       }
