@@ -236,6 +236,20 @@ int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t
                             int32_t seq_len, int32_t head_dim, int32_t relative, int32_t num_bins, int32_t sink,
                             double* hist, sqattn_stream_t stream);
 
+/* ---- decoder-layer row kernels: the caller's side of the operator (model_hub/utils.py) ------------------- */
+
+/* out[r, :] = (x[r, :] * rsqrt(mean(x[r, :]^2) + eps)) * weight, rmsnorm (model_hub/utils.py:14-18); 16-bit rows
+ * with element strides, dim a multiple of 8; x and out may alias. */
+int sqattn_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int32_t dim, int64_t x_row_stride,
+                   int64_t out_row_stride, float eps, int32_t dtype, sqattn_stream_t stream);
+/* apply_rope_with_cos_sin_cache_inplace (model_hub/utils.py:20-106) on the fused QKV projection: the first
+ * num_heads heads (query heads then key heads) of every row [rows, row_stride] are rotated in place with
+ * cos|sin = cos_sin_cache[pos0 + row % seq_len] (fp32 [cache_rows, head_dim]). */
+int sqattn_rope_qk(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads, int32_t head_dim,
+                   const float* cos_sin_cache, int64_t cache_rows, int64_t pos0, int32_t dtype, sqattn_stream_t stream);
+/* silu_and_mul (model_hub/utils.py:4-12): x [rows, 2*inter] -> out [rows, inter] = x[:, inter:] * silu(x[:, :inter]) */
+int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32_t dtype, sqattn_stream_t stream);
+
 /* ---- KV cache block mover (cache_hub/flash_attn_cache.py:7-19, 143-151, 200-227) ---------- */
 
 /* Gather rows [row0, row0+rows) of a [*, row_elems] 16-bit matrix that lives in (pinned) host or device

@@ -99,6 +99,11 @@ SYMBOLS = [
                                      C.c_int32, C.c_void_p, C.c_void_p]),
     ("sqattn_window_histogram", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                           C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    ("sqattn_rmsnorm", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_float,
+                                 C.c_int32, C.c_void_p]),
+    ("sqattn_rope_qk", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
+                                 C.c_int64, C.c_int32, C.c_void_p]),
+    ("sqattn_silu_mul", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]),
     ("sqattn_cache_copy_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
                                          C.c_void_p]),
     ("sqattn_check_device_status", C.c_int, [C.c_void_p]),

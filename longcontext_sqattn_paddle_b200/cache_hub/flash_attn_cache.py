@@ -50,7 +50,8 @@ class flash_attn_cache:
     def __init__(self, valid_start, layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim,
                  dtype, layer_mapping=None, num_gpus=1, model_size=0, device="cuda", force_host: Optional[bool] = None):
         self.valid_start = valid_start
-        self.valid_length = None
+        self.valid_length = None          # device int64 [B]
+        self.valid_length_host = None     # the same numbers on the host (no synchronisation to read them)
         self.layer_num, self.batch_size, self.max_length = layer_num, batch_size, max_length
         self.kv_head, self.num_heads, self.head_dim, self.dtype = num_key_value_heads, num_heads, head_dim, dtype
         self.context = 0
@@ -81,19 +82,24 @@ class flash_attn_cache:
         valid = seq_len - vs
         if self.valid_length is None:
             self.valid_length = torch.full((self.batch_size,), valid, dtype=torch.int64, device=self.device)
+            self.valid_length_host = [valid] * self.batch_size
+        if layer_idx == 0 and self.valid_length_host[start_bdx] != valid:
+            self.valid_length[start_bdx] = valid
+            self.valid_length_host[start_bdx] = valid
         ready = torch.cuda.Event()
         ready.record()
         self.copystream.wait_event(ready)
-        row = self.kv_head * self.head_dim
         for cache, states in ((self.key_cache, key_states), (self.value_cache, value_states)):
-            dst = cache[layer_idx][start_bdx, :valid].reshape(valid, row)
-            src = states[0, vs:vs + valid].to(self.dtype).reshape(valid, row)
+            dst = cache[layer_idx][start_bdx, :valid]                    # [valid, Hkv, D], contiguous
+            src = states[0, vs:vs + valid]                               # may be a strided view of a fused projection
+            if src.dtype != self.dtype:
+                src = src.to(self.dtype)
+            src.record_stream(self.copystream)
             if self.allocated:
                 with torch.cuda.stream(self.copystream):
                     dst.copy_(src, non_blocking=True)
             else:
-                src.record_stream(self.copystream)
-                _copy_rows(dst, src, self.copystream)
+                _copy_rows(dst.flatten(1), src.flatten(1), self.copystream)
         self.copyevents[layer_idx].record(self.copystream)
         if layer_idx == self.layer_num - 1 and start_bdx + bsz == self.batch_size:
             self.context += seq_len
@@ -120,6 +126,7 @@ class flash_attn_cache:
         if layer_idx == self.layer_num - 1:
             self.context += 1
             self.valid_length += 1
+            self.valid_length_host = [x + 1 for x in self.valid_length_host]
         return self.key_cache[layer_idx], self.value_cache[layer_idx]
 
     def decode_attention(self, query, layer_idx, kv_len: int, out_dtype=None):

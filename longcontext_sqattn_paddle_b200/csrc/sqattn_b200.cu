@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "decode.cuh"
+#include "decoder_ops.cuh"
 #include "kmeans.cuh"
 #include "prefill.cuh"
 #include "prep.cuh"
@@ -640,6 +641,55 @@ int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t
     SQ_CUDA(cudaFuncSetAttribute(window_hist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     window_hist_kernel<false><<<grid, 256, smem, stream>>>(p);
   }
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+// ---- decoder-layer row kernels ---------------------------------------------------------------------------
+int sqattn_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int32_t dim, int64_t x_row_stride,
+                   int64_t out_row_stride, float eps, int32_t dtype, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!x || !weight || !out) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (rows <= 0 || rows > 2147483647ll || dim <= 0 || dim % 8 || x_row_stride % 8 || out_row_stride % 8 ||
+      x_row_stride < dim || out_row_stride < dim)
+    return fail(SQATTN_ERR_INVALID_ARG, "rmsnorm: rows %lld dim %d strides %lld %lld (dim and strides must be multiples of 8)",
+                static_cast<long long>(rows), dim, static_cast<long long>(x_row_stride), static_cast<long long>(out_row_stride));
+  if (dtype == SQATTN_BF16)
+    rmsnorm_kernel<true><<<static_cast<unsigned>(rows), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(weight), static_cast<uint8_t*>(out), dim, x_row_stride, out_row_stride, eps);
+  else
+    rmsnorm_kernel<false><<<static_cast<unsigned>(rows), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(weight), static_cast<uint8_t*>(out), dim, x_row_stride, out_row_stride, eps);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_rope_qk(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads, int32_t head_dim,
+                   const float* cos_sin_cache, int64_t cache_rows, int64_t pos0, int32_t dtype, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!qkv || !cos_sin_cache) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (head_dim <= 0 || head_dim % 16) return fail(SQATTN_ERR_UNSUPPORTED, "rope: head_dim %d must be a multiple of 16", head_dim);
+  if (rows <= 0 || seq_len <= 0 || num_heads <= 0 || row_stride % 8 || row_stride < static_cast<int64_t>(num_heads) * head_dim)
+    return fail(SQATTN_ERR_INVALID_ARG, "rope: bad sizes");
+  if (pos0 < 0 || pos0 + seq_len > cache_rows)
+    return fail(SQATTN_ERR_INVALID_ARG, "rope: positions %lld..%lld exceed the cos/sin cache (%lld rows)",
+                static_cast<long long>(pos0), static_cast<long long>(pos0 + seq_len), static_cast<long long>(cache_rows));
+  const int grid = elementwise_grid(rows * num_heads * (head_dim / 16), 256);
+  if (dtype == SQATTN_BF16)
+    rope_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(qkv), row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, pos0);
+  else
+    rope_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(qkv), row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, pos0);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32_t dtype, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!x || !out) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (rows <= 0 || inter <= 0 || inter % 8) return fail(SQATTN_ERR_INVALID_ARG, "silu_mul: rows %lld inter %d", static_cast<long long>(rows), inter);
+  const int grid = elementwise_grid(rows * (inter / 8), 256);
+  if (dtype == SQATTN_BF16) silu_mul_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), rows, inter);
+  else silu_mul_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), rows, inter);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }

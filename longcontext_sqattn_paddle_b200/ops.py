@@ -244,3 +244,40 @@ def decode_static_scratch(q, k, v, out, *, layout: str = "HND", lse: Optional[to
     a.p_fp8, a.q_is_scaled, a.num_splits, a.reference_tail = int(p_fp8), int(q_is_scaled), int(num_splits), int(reference_tail)
     L.check(L.lib.sqattn_decode_static_scratch(C.byref(a), _stream()))
     return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sqattn_rmsnorm over the last dimension of x [..., dim] (rows may be strided); out may be x itself."""
+    _require_cuda(x, weight)
+    dim = x.shape[-1]
+    x2 = x.reshape(-1, dim) if x.dim() != 2 else x
+    assert x2.stride(1) == 1 and weight.is_contiguous() and weight.numel() == dim
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device) if out is None else out
+    o2 = out.reshape(-1, dim) if out.dim() != 2 else out
+    assert o2.stride(1) == 1 and o2.shape == x2.shape
+    assert o2.data_ptr() == out.data_ptr(), "out must be viewable as [rows, dim] without a copy"
+    L.check(L.lib.sqattn_rmsnorm(x2.data_ptr(), weight.data_ptr(), o2.data_ptr(), x2.shape[0], dim, x2.stride(0),
+                                 o2.stride(0), float(eps), _dt(x.dtype), _stream()))
+    return out
+
+
+def rope_qk(qkv: torch.Tensor, seq_len: int, num_heads: int, head_dim: int, cos_sin_cache: torch.Tensor, pos0: int):
+    """sqattn_rope_qk: rotate the first num_heads heads of every row of the fused projection qkv [rows, width]
+    in place; row r takes position pos0 + r % seq_len of cos_sin_cache [max_len, head_dim] (fp32)."""
+    _require_cuda(qkv, cos_sin_cache)
+    assert qkv.dim() == 2 and qkv.stride(1) == 1
+    assert cos_sin_cache.dtype == torch.float32 and cos_sin_cache.is_contiguous() and cos_sin_cache.shape[1] == head_dim
+    L.check(L.lib.sqattn_rope_qk(qkv.data_ptr(), qkv.stride(0), qkv.shape[0], int(seq_len), int(num_heads), int(head_dim),
+                                 cos_sin_cache.data_ptr(), cos_sin_cache.shape[0], int(pos0), _dt(qkv.dtype), _stream()))
+    return qkv
+
+
+def silu_mul(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sqattn_silu_mul: x [..., 2*inter] contiguous -> [..., inter]."""
+    _require_cuda(x)
+    assert x.is_contiguous() and x.shape[-1] % 2 == 0
+    inter = x.shape[-1] // 2
+    out = torch.empty(*x.shape[:-1], inter, dtype=x.dtype, device=x.device) if out is None else out
+    assert out.is_contiguous()
+    L.check(L.lib.sqattn_silu_mul(x.data_ptr(), out.data_ptr(), x.numel() // (2 * inter), inter, _dt(x.dtype), _stream()))
+    return out
