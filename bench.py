@@ -367,6 +367,27 @@ def run_ours(args):
             extra["decode_1m"] = {"error": repr(e)}
         ops.check_device_status()
 
+    else:
+        # every rank times the attention kernel on its own query shard against the gathered K/V; the slowest rank
+        # sets the time, the figure is per GPU
+        be = sqdist.CudaBackend()
+        sums = be.k_column_sums(dk)
+        dist.all_reduce(sums)
+        q8, k8s, v8s = be.prep(dq, dk, dv, (sums / float(n_total)).contiguous(), "int", "int")
+        k_full = torch.empty(1, n_total, HKV, D, dtype=k8s.dtype, device=dev)
+        v_full = torch.empty(1, n_total, HKV, D, dtype=v8s.dtype, device=dev)
+        dist.all_gather_into_tensor(k_full.view(n_total, HKV, D), k8s.view(SEQ_PER_GPU, HKV, D))
+        dist.all_gather_into_tensor(v_full.view(n_total, HKV, D), v8s.view(SEQ_PER_GPU, HKV, D))
+        kern = lambda: be.windowed_prefill(q8, k_full, v_full, r, r, SINK, rank * SEQ_PER_GPU, 0)
+        for _ in range(3):
+            kern()
+        kms = timed(kern, args.steps) / args.steps
+        ach = flops_total / world / (kms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "prefill_kernel<128> (relative windows), per GPU, slowest rank",
+                "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"],
+                "peak_source": peaks["src"], "ms_per_launch": kms, "traffic": None}
+        ops.check_device_status()
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_sample(0, SEQ_PER_GPU, nblocks=16)
@@ -427,6 +448,116 @@ def run_kernel_only(args):
     print(json.dumps({"kernel": args.kernel_only, "seq": n, "ms_per_launch": ms, "rate": work / (ms * 1e-3), "unit": unit}))
 
 
+def run_decoder(args):
+    """The operator inside its caller: a random-weight decoder of the Qwen2.5-7B geometry.
+    --workload ttft: prefill of --seq uniform-random token ids (sharded over the ranks, sequence parallel), time to
+    the first token's logits.  --workload decode_model: decode steps at a --seq-token context (cache filled with
+    N(0,1) keys/values), one new token per step through all layers."""
+    import torch.distributed as dist
+
+    from longcontext_sqattn_paddle_b200.model_hub import DecoderConfig, RandomInitDecoder, install_sequence_parallel
+    from longcontext_sqattn_paddle_b200.sqattn import process_model
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = DecoderConfig.qwen2_5_7b(num_hidden_layers=args.layers)
+    n_total = args.seq
+
+    class Args:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", True
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_ms(ms):
+        t = torch.tensor([ms], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    if args.workload == "ttft":
+        if n_total % world or (world > 1 and (n_total // world) % 128):
+            raise SystemExit("--seq must split into shards of a multiple of 128 tokens")
+        ns = n_total // world
+        model = RandomInitDecoder(cfg, max_length=n_total + 8, device=dev, seed=0, seq_shard=(rank, world))
+        windows = {i: {"bit8": [RATIO] * HQ, "bit4": [RATIO] * HQ, "sink": SINK} for i in range(cfg.num_hidden_layers)}
+        if world > 1:
+            install_sequence_parallel(model, windows, Args())
+        else:
+            process_model(model, "SQAttn", windows, Args())
+        g = torch.Generator().manual_seed(7)
+        ids = torch.randint(0, cfg.vocab_size, (1, n_total), generator=g)[:, rank * ns:(rank + 1) * ns].pin_memory()
+        model.batch_size, model.max_new_length = 1, 8
+        times = []
+        for it in range(args.warmup + args.steps):
+            model.init_kv_cache(ns, (0,))
+            sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            logits = model.prefill_forward(ids.to(dev, non_blocking=True))
+            tok = logits.argmax(dim=-1)
+            e1.record()
+            sync_all()
+            if it >= args.warmup:
+                times.append(max_ms(e0.elapsed_time(e1)))
+            model.kv_cache = None
+        from longcontext_sqattn_paddle_b200 import ops
+        ops.check_device_status()
+        if rank == 0:
+            ms = sum(times) / len(times)
+            print(json.dumps({"workload": "decoder_prefill_ttft", "metric": "ttft_ms", "value": ms, "unit": "ms",
+                              "higher_is_better": False, "n_gpus": world, "seq_len": n_total, "layers": cfg.num_hidden_layers,
+                              "tokens_per_s": n_total / (ms * 1e-3), "steps": args.steps, "warmup": args.warmup,
+                              "parallelism": f"sp{world}", "data": "synthetic uniform-random token ids, random weights",
+                              "window": {"sink": SINK, "ratio": RATIO}, "dtype": "bf16"}))
+    else:
+        new_tokens = args.warmup + args.steps + 1
+        model = RandomInitDecoder(cfg, max_length=n_total + new_tokens, device=dev, seed=0)
+        model.batch_size, model.max_new_length = 1, new_tokens
+        model.init_kv_cache(n_total, (0,))
+        kc = model.kv_cache
+        if not kc.allocated:
+            raise SystemExit("the cache does not fit this GPU")
+        for ldx in range(cfg.num_hidden_layers):
+            kc.key_cache[ldx].normal_()
+            kc.value_cache[ldx].normal_()
+        kc.valid_length = torch.full((1,), n_total, dtype=torch.int64, device=dev)
+        kc.valid_length_host = [n_total]
+        kc.context = n_total
+        tok = torch.zeros(1, 1, dtype=torch.int64, device=dev)
+        for _ in range(args.warmup):
+            tok = model.decode_forward(tok).argmax(dim=-1)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            tok = model.decode_forward(tok).argmax(dim=-1)
+        e1.record()
+        sync_all()
+        from longcontext_sqattn_paddle_b200 import ops
+        ops.check_device_status()
+        ms = e0.elapsed_time(e1) / args.steps
+        kv_bytes = 2.0 * cfg.num_hidden_layers * HKV * D * 2 * n_total
+        w_bytes = 2.0 * sum(t.numel() for l in model.layers for t in (l.wqkv, l.wo, l.gate_up_proj, l.down_proj)) \
+            + 2.0 * model.lm_head.numel()
+        print(json.dumps({"workload": "decoder_decode", "metric": "decode_ms_per_token", "value": ms, "unit": "ms",
+                          "higher_is_better": False, "n_gpus": 1, "context": n_total, "layers": cfg.num_hidden_layers,
+                          "tokens_per_s": 1e3 / ms, "hbm_gbs": (kv_bytes + w_bytes) / (ms * 1e-3) / 1e9,
+                          "kv_gb": kv_bytes / 1e9, "weights_gb": w_bytes / 1e9, "steps": args.steps,
+                          "warmup": args.warmup, "data": "synthetic N(0,1) cache, random weights", "dtype": "bf16"}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -436,10 +567,17 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode"],
                     help="launch only this kernel --steps times on the bench tensors (for profiler captures)")
-    ap.add_argument("--seq", type=int, default=SEQ_PER_GPU, help="sequence length for --kernel-only")
+    ap.add_argument("--seq", type=int, default=None, help="sequence length for --kernel-only / --workload")
+    ap.add_argument("--workload", default="operator", choices=["operator", "ttft", "decode_model"],
+                    help="operator: the headline line; ttft / decode_model: the operator inside the decoder stand-in")
+    ap.add_argument("--layers", type=int, default=28, help="decoder layers for --workload ttft / decode_model")
     args = ap.parse_args()
+    if args.seq is None:
+        args.seq = {"operator": SEQ_PER_GPU, "ttft": 131072, "decode_model": 1048576}[args.workload]
     if args.kernel_only:
         run_kernel_only(args)
+    elif args.workload != "operator":
+        run_decoder(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
