@@ -17,6 +17,7 @@ constexpr int kMaxHeads = 128;
 constexpr int kBlockM = 128;  // query rows per CTA (tcgen05 M)
 constexpr int kBlockN = 64;   // keys per step (the reference BLOCK_N)
 constexpr int kMaxSegs = 12;
+constexpr float kLazyLog2 = 8.0f;  // O is rescaled only when a row's maximum has moved by more than 2^8
 
 // segment flags
 constexpr int kSegAct0 = 1;   // rows 0..63 of the CTA take part
@@ -130,7 +131,7 @@ struct PrefillSmem {
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kVOff = kKOff + kKStages * kKBytes;
   static constexpr int kBarOff = kVOff + kVStages * kVBytes;
-  // barriers: q_full, q_empty, k_full[KS], v_full[VS], s_full[2], p_full[2], o_done[2]
+  // barriers: q_full, q_empty, k_full[KS], v_full[VS], s_full[2], p_full[2], o_tail[2]
   static constexpr int kNumBars = 2 + kKStages + kVStages + 2 + 2 + 2;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
   static constexpr int kSegOff = kMiscOff + 16;  // tmem base, abort flag, nseg
@@ -186,9 +187,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
   const uint32_t q_s = sbase + L::kQOff, k_s = sbase + L::kKOff, v_s = sbase + L::kVOff;
   const uint32_t bars = sbase + L::kBarOff;
   const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
-  static_assert(KS == 2 && VS == 2, "K/V stages are tied to the two S buffers");
+  static_assert(KS == 2 && VS == 3, "K stages follow the two S buffers; V has one stage more");
   const uint32_t bar_k_full = bars + 16, bar_v_full = bar_k_full + 8 * KS;
-  const uint32_t bar_s_full = bar_v_full + 8 * VS, bar_p_full = bar_s_full + 16, bar_o_done = bar_p_full + 16;
+  const uint32_t bar_s_full = bar_v_full + 8 * VS, bar_p_full = bar_s_full + 16, bar_o_tail = bar_p_full + 16;
   volatile uint32_t* tmem_base_s = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
   volatile int* nseg_s = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 8);
@@ -210,8 +211,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     for (int i = 0; i < KS; ++i) mbar_init(bar_k_full + 8 * i, 1);
     for (int i = 0; i < VS; ++i) mbar_init(bar_v_full + 8 * i, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_s_full + 8 * i, 1); mbar_init(bar_p_full + 8 * i, 128); }
-    mbar_init(bar_o_done, 1);
-    mbar_init(bar_o_done + 8, 1);
+    mbar_init(bar_o_tail, 1);
+    mbar_init(bar_o_tail + 8, 1);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -229,9 +230,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    // K stage (i & 1) is free again when QK^T of step i-2 has completed (s_full of that step), V stage (i & 1)
-    // when P V of step i-2 has completed (o_done): the completion barriers double as "empty" barriers, which
-    // saves the issuing threads two tcgen05.commit per step.
+    // The issuer commits once per step, after Q K^T of step i (barrier s_full(i)); at that point P V of step i-2
+    // and everything before it has completed as well (one thread's MMAs complete in issue order).  So s_full
+    // doubles as the "stage is free" signal: K stage i & 1 is free at s_full(i-2), V stage i % 3 (last read by
+    // P V of step i-3) at s_full(i-1).
     if (lane == 0) {
       tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_v);
       int q_loads = 0;
@@ -248,7 +250,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
           for (int h = 0; h < D / 64; ++h) tma_load_4d(q_s + h * (kBlockM * 128), tq, bar_q_full, h * 64, blk * kBlockM, head, bi);
           ++q_loads;
         }
-        const int st = i & 1;
+        const int st = i & 1, vst = i % 3;
         if (i >= 2) ok = mbar_wait(bar_s_full + 8 * st, ((i - 2) >> 1) & 1, cta_abort, 102);
         if (!ok) break;
         SQ_STAMP(i, 12);
@@ -257,22 +259,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
 #pragma unroll
         for (int h = 0; h < D / 64; ++h)
           tma_load_4d(k_s + st * L::kKBytes + h * (kBlockN * 128), tk, bar_k_full + 8 * st, h * 64, it.key0(), kvh, bi);
-        if (i >= 2) ok = mbar_wait(bar_o_done + 8 * st, ((i - 2) >> 1) & 1, cta_abort, 103);
+        if (i >= 3) ok = mbar_wait(bar_s_full + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, cta_abort, 103);
         if (!ok) break;
         SQ_STAMP(i, 13);
-        mbar_expect_tx(bar_v_full + 8 * st, L::kVBytes);
+        mbar_expect_tx(bar_v_full + 8 * vst, L::kVBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h)
-          tma_load_4d(v_s + st * L::kVBytes + h * (kBlockN * 128), &tm_v, bar_v_full + 8 * st, h * 64, it.key0(), kvh, bi);
+          tma_load_4d(v_s + vst * L::kVBytes + h * (kBlockN * 128), &tm_v, bar_v_full + 8 * vst, h * 64, it.key0(), kvh, bi);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ tcgen05 issuer
     // Measured on B200: one tcgen05.mma costs the issuing thread ~107 cycles whatever its size (and an N = 64
-    // instruction occupies the tensor pipe as long as an N = 128 one), one tcgen05.commit ~350 cycles plus ~85
-    // for each further commit behind it.  With 12 MMAs per step this thread is the critical path of the
-    // kernel, so it does nothing else: descriptors are built once, and there is exactly one commit per batch
-    // (the completion barriers double as the producer's "stage is free" barriers).
+    // instruction occupies the tensor pipe as long as an N = 128 one), one tcgen05.commit ~350 cycles.  With 12
+    // MMAs per step this thread is the critical path of the kernel, so it does nothing else: descriptors are
+    // built once and there is ONE commit per step, behind Q K^T; since one thread's MMAs complete in issue
+    // order that commit also reports P V of two steps earlier, which is all the other warps need to know.
     // Issue order QK(i+1), PV(i): S buffer (i+1)&1 still holds P(i-1), which PV(i-1), issued earlier by this
     // same thread, consumes first (the tensor pipe executes one thread's MMAs in issue order).
     if (lane == 0) {
@@ -318,20 +320,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         ok = mbar_wait(bar_p_full + 8 * st, (i >> 1) & 1, cta_abort, 113);
         if (!ok) break;
         SQ_STAMP(i, 2);
-        ok = mbar_wait(bar_v_full + 8 * st, (i >> 1) & 1, cta_abort, 114);
+        const int vst = i % 3;
+        ok = mbar_wait(bar_v_full + 8 * vst, (i / 3) & 1, cta_abort, 114);
         if (!ok) break;
         tc_fence_after();
         const uint32_t p_tmem = tmem + st * kBlockN;
-        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(st) * (L::kVBytes >> 4);
+        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(vst) * (L::kVBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // V tile: [64 keys][64 d] 128-byte rows per d-half; MN-major B operand: 64-d chunks 8 KB apart
           // (leading offset), 8-key groups 1 KB apart (stride offset); 16 keys per MMA = 2 KB.
           mma_ts(tmem + kOCol, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc_pv, (i > 0 || kk > 0));
         }
-        // two alternating barriers: a waiter that is up to two steps behind the tensor pipe can still tell the
-        // phases apart by parity
-        tc_commit(bar_o_done + 8 * st);
+        // Completion of P V(i) is reported by the commit behind Q K^T(i+2); only the last two steps, which no
+        // later Q K^T follows, get a commit of their own (slot 0: last step, slot 1: the one before).
+        if (i + 2 >= nsteps) tc_commit(bar_o_tail + 8 * (nsteps - 1 - i));
         SQ_STAMP(i, 4);
       }
     }
@@ -343,7 +346,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     const int row_local = blk * kBlockM + row_in_tile;
     const int row = row_local + p.blk0 * kBlockM;  // position in the whole sequence (causal mask)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    float m_i = -INFINITY, l_i = 1.0f;
+    float m_i = -INFINITY, base = -INFINITY, l_i = 1.0f;  // running maximum; reference of P, l_i and O
     bool ok = true;
     int i = 0;
     for (StepIter it(segs, nseg); ok && !it.done(); it.next(), ++i) {
@@ -380,8 +383,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         }
         mx0 = max3(mx0, x[60], x[61]); mx1 = max3(mx1, x[62], x[63]);
         const float m_new = fmaxf(max3(m_i, mx0, mx1), fmaxf(mx2, mx3));
-        alpha = ex2_approx(m_i - m_new);
-        const uint64_t m2 = f32x2_pack(m_new, m_new);
+        // P, l and O are kept relative to `base`, which follows the running maximum only when it has moved by
+        // more than kLazyLog2 (so P <= 2^kLazyLog2): O then needs its rescale (a wait for the previous P V plus a
+        // TMEM round trip) a few times per row instead of whenever the maximum moves.  Steps whose P is rounded
+        // through e4m3 keep base == running maximum, i.e. p <= 1 as the rounding rule expects.
+        const float thr = (flags & kSegFp8) ? 0.0f : kLazyLog2;
+        if (m_new > base + thr) {
+          alpha = ex2_approx(base - m_new);
+          base = m_new;
+        }
+        const uint64_t m2 = f32x2_pack(base, base);
         uint64_t sa = f32x2_pack(0.0f, 0.0f), sb = sa;
 #pragma unroll
         for (int c = 0; c < 64; c += 4) {
@@ -413,7 +424,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       // acc *= alpha: O lives in TMEM and is rescaled only when some row of this warp moved its maximum
       // (alpha == 1 exactly otherwise, so skipping is bit-identical).
       if (__any_sync(0xffffffffu, alpha != 1.0f) && i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_o_done + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, cta_abort, 122));
+        // P V(i-1) has completed when Q K^T(i+1) has (same issuing thread, in order); the last step waits for the
+        // commit that follows P V of the step before it
+        if (i + 1 < nsteps) ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1, cta_abort, 122));
+        else ok = __all_sync(0xffffffffu, mbar_wait(bar_o_tail + 8, 0, cta_abort, 122));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
@@ -435,7 +449,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * (i & 1));
     }
-    if (ok && nsteps > 0) ok = mbar_wait(bar_o_done + 8 * ((nsteps - 1) & 1), ((nsteps - 1) >> 1) & 1, cta_abort, 123);
+    if (ok && nsteps > 0) ok = mbar_wait(bar_o_tail, 0, cta_abort, 123);
     ok = __all_sync(0xffffffffu, ok);
     if (ok && nsteps > 0) {
       tc_fence_after();
@@ -461,7 +475,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         }
       }
       if (p.lse && in_range)
-        p.lse[(static_cast<long long>(bi) * p.hq + head) * p.n + row_local] = log2f(l_i) + m_i;
+        p.lse[(static_cast<long long>(bi) * p.hq + head) * p.n + row_local] = log2f(l_i) + base;
     }
     tc_fence_before();
   }
