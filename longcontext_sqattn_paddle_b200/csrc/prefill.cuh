@@ -352,9 +352,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     for (StepIter it(segs, nseg); ok && !it.done(); it.next(), ++i) {
       const int flags = it.flags();
       const uint32_t s_tmem = tmem + lane_addr + (i & 1) * kBlockN;
+      if (warp == 2 && lane == 0) SQ_STAMP(i, 5);
       ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + 8 * (i & 1), (i >> 1) & 1, cta_abort, 121));
       if (!ok) break;
       tc_fence_after();
+      if (warp == 2 && lane == 0) SQ_STAMP(i, 6);
       uint32_t pk[32];
       float alpha = 1.0f;
       if (flags & half_bit) {
@@ -362,6 +364,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         tmem_ld32(s_tmem, r0);
         tmem_ld32(s_tmem + 32, r1);
         tmem_wait_ld();
+        if (warp == 2 && lane == 0) SQ_STAMP(i, 7);
         float x[64];
 #pragma unroll
         for (int c = 0; c < 32; ++c) { x[c] = __uint_as_float(r0[c]); x[32 + c] = __uint_as_float(r1[c]); }
@@ -408,6 +411,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         f32x2_unpack(sb, s2, s3);
         const float sum = (s0 + s1) + (s2 + s3);
         l_i = l_i * alpha + sum;
+        if (warp == 2 && lane == 0) SQ_STAMP(i, 9);
         m_i = m_new;
         if (flags & kSegFp8) {
 #pragma unroll
@@ -448,6 +452,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * (i & 1));
+      if (warp == 2 && lane == 0) SQ_STAMP(i, 11);
     }
     if (ok && nsteps > 0) ok = mbar_wait(bar_o_tail, 0, cta_abort, 123);
     ok = __all_sync(0xffffffffu, ok);

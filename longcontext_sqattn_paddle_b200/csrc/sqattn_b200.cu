@@ -9,7 +9,6 @@
 #include "decoder_ops.cuh"
 #include "kmeans.cuh"
 #include "prefill.cuh"
-#include "prefill_wide.cuh"
 #include "prep.cuh"
 #include "retrieval.cuh"
 #include "window_search.cuh"
@@ -157,22 +156,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
       prefill_kernel<D, false, KS, VS, MINB><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);   \
     }                                                                                                                    \
   } while (0)
-  static const int variant = [] {
-    const char* e = getenv("SQATTN_PREFILL_VARIANT");  // "wide": the experimental kernel with 128-key Q K^T tiles (slower; kept for study)
-    return (e && !strcmp(e, "wide")) ? 1 : 0;
-  }();
-  if (variant == 1) {
-    using LW = WideSmem<D>;
-    if (dump || dump_t) {
-      SQ_CUDA(cudaFuncSetAttribute(prefill_wide_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, LW::kDynBytes));
-      prefill_wide_kernel<D, true><<<static_cast<unsigned>(grid), 352, LW::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);
-    } else {
-      SQ_CUDA(cudaFuncSetAttribute(prefill_wide_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, LW::kDynBytes));
-      prefill_wide_kernel<D, false><<<static_cast<unsigned>(grid), 352, LW::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);
-    }
-  } else {
-    SQ_LAUNCH_PREFILL(2, 3, 2);  // two K stages (tied to the two S buffers), three V stages, two CTAs per SM
-  }
+  SQ_LAUNCH_PREFILL(2, 3, 2);  // two K stages (tied to the two S buffers), three V stages, two CTAs per SM
 #undef SQ_LAUNCH_PREFILL
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
