@@ -162,6 +162,25 @@ __device__ __forceinline__ float fake_quant_value(float x, float absmax, int qty
   return s * scale;
 }
 
+// Integer grid, fast path for 8 values of one row: q = x * (1/scale) is within 2e-5 of the exact quotient
+// x / scale (|q| <= qmax * (1 + 2^-22), so the clamp of the reference never acts), hence unless q lies within
+// 1e-4 of a half-integer its nearest integer IS round(x / scale) in either rounding mode; a group with such a
+// value (rare) is redone with exact divisions.  Results are identical to fake_quant_value(..., INT, ...).
+__device__ __forceinline__ void fake_quant_int8x(const float (&x)[8], float absmax, float qmax, int half_even, float (&out)[8]) {
+  const float scale = __fdiv_rn(absmax, qmax), inv = __fdiv_rn(1.0f, scale);
+  float worst = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float q = x[i] * inv, r = rintf(q);
+    worst = fmaxf(worst, fabsf(q - r));
+    out[i] = r * scale;
+  }
+  if (worst > 0.4999f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = fake_quant_value(x[i], absmax, SQATTN_QTYPE_INT, qmax, half_even);
+  }
+}
+
 // Per-token fake-quant of Q or K.  Input [B,N,H,D] via strides, outputs contiguous [B,H,N,D].
 // kIsK: subtract the (dtype-rounded) sequence mean first, no scaling of the result.
 // Q: results are multiplied by 1/sqrt(D)*log2e in the input dtype.
@@ -210,17 +229,25 @@ quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uint8_t* out4, OutS
       amax = fmaxf(amax, 1e-5f);
       if (live[u]) {
         float g[8];
+        if (qtype == SQATTN_QTYPE_INT) {
+          fake_quant_int8x(f, amax, 127.0f, half_even, g);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
-          if (!kIsK) g[i] *= q_scale;
+          for (int i = 0; i < 8; ++i) g[i] = to_f32<BF16>(from_f32<BF16>(g[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
+        }
+        if (!kIsK) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) g[i] *= q_scale;
         }
         const long long ooff = out_base + static_cast<long long>(n0 + u * rows_per_block) * os.sn * 2;
         *reinterpret_cast<uint4*>(out8 + ooff) = pack8<BF16>(g);
         if (out4) {
+          fake_quant_int8x(f, amax, 7.0f, half_even, g);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, SQATTN_QTYPE_INT, 7.0f, half_even)));
+            g[i] = to_f32<BF16>(from_f32<BF16>(g[i]));
             if (!kIsK) g[i] *= q_scale;
           }
           *reinterpret_cast<uint4*>(out4 + ooff) = pack8<BF16>(g);
