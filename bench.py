@@ -570,6 +570,120 @@ def run_decoder(args):
         dist.destroy_process_group()
 
 
+def run_decode_variants(args):
+    """Decode-side workloads next to the headline line.
+    --workload decode_sp: one decode step = 28 layers of split-KV attention over a --seq-token context whose keys
+      are sharded over the ranks (partial O + LSE per rank, one all-gather, one merge kernel per layer).
+    --workload decode_hybrid: --layers layers of a --seq-token cache with 75 % of the blocks in pinned host memory,
+      staged to the GPU by a side stream while the previous layer computes.
+    --workload retrieval: ragged batch of 16 sequences (context log-uniform in [8K, 256K]), Llama-3-8B geometry,
+      keys clustered per KV head into len/64 centroids (10 Lloyd iterations), 4096-token budget, FP8 P."""
+    import math
+    import torch.distributed as dist
+
+    from longcontext_sqattn_paddle_b200 import dist as sqdist
+    from longcontext_sqattn_paddle_b200 import ops
+    from longcontext_sqattn_paddle_b200.cache_hub import ClusteredKV, HybridKVCache, RaggedClusteredDecoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    res = None
+    if args.workload == "decode_sp":
+        n_total, nl = args.seq, args.layers
+        ls = n_total // world
+        layers = [(torch.randn(1, HKV, ls, D, device=dev, dtype=torch.bfloat16),
+                   torch.randn(1, HKV, ls, D, device=dev, dtype=torch.bfloat16)) for _ in range(nl)]
+        g = torch.Generator(device=dev).manual_seed(5)
+        qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16, generator=g)
+
+        def step():
+            for kk, vv in layers:
+                sqdist.sp_decode(qd, kk, vv, out_dtype=torch.bfloat16)
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        ms = timed(step, args.steps)
+        nbytes = nl * 2.0 * HKV * n_total * D * 2
+        res = {"workload": "decode_split_kv", "metric": "decode_attention_ms_per_token", "value": ms, "unit": "ms",
+               "higher_is_better": False, "n_gpus": world, "context": n_total, "layers": nl,
+               "aggregate_gb_per_s": nbytes / (ms * 1e-3) / 1e9, "kv_gb_total": nbytes / 1e9, "steps": args.steps,
+               "parallelism": f"kv-shard x{world}", "data": "synthetic N(0,1) cache", "dtype": "bf16"}
+    elif args.workload == "decode_hybrid":
+        n_total, nl = args.seq, args.layers
+        cache = HybridKVCache(nl, 1, n_total, HKV, D, torch.bfloat16, gpu_fraction=0.25, device=dev)
+        for ldx in range(nl):
+            cache.k_res[ldx].normal_()
+            cache.v_res[ldx].normal_()
+            for host in (cache.k_host[ldx], cache.v_host[ldx]):  # filled from the GPU: a CPU generator is slow
+                host.copy_(torch.randn(host.shape, device=dev, dtype=torch.bfloat16))
+        qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16)
+
+        def step():
+            cache.prefetch(0)
+            for ldx in range(nl):
+                cache.decode_attention(qd, ldx)
+
+        for _ in range(2):
+            step()
+        ms = timed(step, max(2, min(args.steps, 5)))
+        host_bytes = nl * 2.0 * HKV * cache.host_tokens * D * 2
+        res = {"workload": "decode_hybrid_cache", "metric": "decode_attention_ms_per_token", "value": ms, "unit": "ms",
+               "higher_is_better": False, "n_gpus": 1, "context": n_total, "layers": nl, "host_fraction": cache.host_tokens / n_total,
+               "host_gb_per_step": host_bytes / 1e9, "h2d_gb_per_s": host_bytes / (ms * 1e-3) / 1e9,
+               "data": "synthetic N(0,1) cache", "dtype": "bf16"}
+    else:
+        hq, hkv = 32, 8
+        g = torch.Generator().manual_seed(11)
+        u = torch.rand(16, generator=g)
+        lens = [int(math.exp(math.log(8192) + float(x) * (math.log(262144) - math.log(8192)))) // 64 * 64 for x in u]
+        t0 = time.perf_counter()
+        caches = []
+        for ln in lens:
+            caches.append(ClusteredKV(torch.randn(hkv, ln, D, device=dev, dtype=torch.bfloat16),
+                                      torch.randn(hkv, ln, D, device=dev, dtype=torch.bfloat16), 64, 10))
+        torch.cuda.synchronize()
+        build_s = time.perf_counter() - t0
+        dec = RaggedClusteredDecoder(caches, budget=4096, p_fp8=True)
+        qd = torch.randn(16, hq, 1, D, device=dev, dtype=torch.bfloat16)
+        for _ in range(max(args.warmup, 3)):
+            dec.step(qd)
+        ms = timed(lambda: dec.step(qd), args.steps)
+        res = {"workload": "ragged_clustered_decode", "metric": "tokens_per_s", "value": 16 / (ms * 1e-3), "unit": "tokens/s",
+               "higher_is_better": True, "n_gpus": 1, "ms_per_step": ms, "sequences": 16, "context_lengths": lens,
+               "geometry": "32 q / 8 kv heads, head_dim 128", "budget": 4096, "p_fp8": True,
+               "cluster_build_s": build_s, "clustered_tokens": sum(lens), "attention_layers_per_step": 1,
+               "data": "synthetic N(0,1) keys/values", "dtype": "bf16"}
+    ops.check_device_status()
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -580,16 +694,18 @@ def main():
     ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode"],
                     help="launch only this kernel --steps times on the bench tensors (for profiler captures)")
     ap.add_argument("--seq", type=int, default=None, help="sequence length for --kernel-only / --workload")
-    ap.add_argument("--workload", default="operator", choices=["operator", "ttft", "decode_model"],
+    ap.add_argument("--workload", default="operator", choices=["operator", "ttft", "decode_model", "decode_sp", "decode_hybrid", "retrieval"],
                     help="operator: the headline line; ttft / decode_model: the operator inside the decoder stand-in")
     ap.add_argument("--layers", type=int, default=28, help="decoder layers for --workload ttft / decode_model")
     args = ap.parse_args()
     if args.seq is None:
-        args.seq = {"operator": SEQ_PER_GPU, "ttft": 131072, "decode_model": 1048576}[args.workload]
+        args.seq = {"operator": SEQ_PER_GPU, "ttft": 131072}.get(args.workload, 1048576)
     if args.kernel_only:
         run_kernel_only(args)
-    elif args.workload != "operator":
+    elif args.workload in ("ttft", "decode_model"):
         run_decoder(args)
+    elif args.workload != "operator":
+        run_decode_variants(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

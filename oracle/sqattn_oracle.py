@@ -333,8 +333,8 @@ def windowed_prefill(q_int8, k_int8, q_int4, k_int4, v, win8, win4, sink_size: i
         for blk in blk_list:
             qs, qe = blk * block_m, (blk + 1) * block_m
             rows = torch.arange(qs, qe)
-            q8b = _load_rows(q8[:, hq], qs, block_m, n)
-            q4b = _load_rows(q4[:, hq], qs, block_m, n)
+            q8b = _load_rows(q8, qs, block_m, n)[:, hq]
+            q4b = _load_rows(q4, qs, block_m, n)[:, hq]
             acc = torch.zeros(b, len(heads), block_m, d)
             l_i = torch.ones(b, len(heads), block_m)
             m_i = torch.full((b, len(heads), block_m), float("-inf"))
@@ -342,8 +342,8 @@ def windowed_prefill(q_int8, k_int8, q_int4, k_int4, v, win8, win4, sink_size: i
                 qb, kk = (q4b, k4) if stage == 2 else (q8b, k8)
                 fp8 = p_fp8_mode == "all" or (p_fp8_mode == "stage2" and stage == 2)
                 for start_n in range(lo, hi, block_n):
-                    k_t = _load_rows(kk[:, hk], start_n, block_n, kv_len)
-                    v_t = _load_rows(vv[:, hk], start_n, block_n, kv_len)
+                    k_t = _load_rows(kk, start_n, block_n, kv_len)[:, hk]
+                    v_t = _load_rows(vv, start_n, block_n, kv_len)[:, hk]
                     acc, l_i, m_i = _tile_step((acc, l_i, m_i), qb, k_t, v_t, rows, start_n,
                                                block_n, stage == 4, fp8)
             valid = min(qe, n) - qs
@@ -384,8 +384,8 @@ def dense_causal(q, k, v, *, tensor_layout: str = "HND", output_dtype=torch.floa
         m_i = torch.full((b, h, block_m), float("-inf"))
         for masked, lo, hi in ((False, 0, qs), (True, qs, qe)):
             for start_n in range(lo, hi, block_n):
-                k_t = _load_rows(kh[:, hk], start_n, block_n, kv_len)
-                v_t = _load_rows(vh[:, hk], start_n, block_n, kv_len)
+                k_t = _load_rows(kh, start_n, block_n, kv_len)[:, hk]
+                v_t = _load_rows(vh, start_n, block_n, kv_len)[:, hk]
                 acc, l_i, m_i = _tile_step((acc, l_i, m_i), qb, k_t, v_t, rows, start_n, block_n,
                                            masked, is_P_fp8_quant)
         valid = min(qe, n) - qs
