@@ -59,6 +59,34 @@ def test_dense_causal_nhd_batch(sq):
     _cmp(o.permute(0, 2, 1, 3), lse, ro.permute(0, 2, 1, 3), rlse)
 
 
+@pytest.mark.parametrize("mode", ["dense", "relative"])
+def test_growing_scores_exercise_the_deferred_rescale(sq, mode):
+    """Scores that keep growing along the keys: the row maximum moves by 2 to 5 octaves from one 64-key tile to
+    the next, so the kernel's reference point for P, the row sum and O (which follows the maximum only after a
+    2^8 move) is re-based every few tiles and O is rescaled in TMEM each time.  N(0,1) inputs never reach that
+    path after the first tile."""
+    n, d, hq, hkv = 1536, 128, 4, 2
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(21)
+    u = torch.nn.functional.normalize(torch.randn(d, generator=g), dim=0)
+    steps = torch.randint(2, 6, (n // 64,), generator=g).float().cumsum(0)          # octaves per tile, cumulative
+    ramp = steps.repeat_interleave(64)[:n]                                            # target log2-score per key
+    # q rows all have projection ~ sqrt(d)/log2(e) on u, so s = q.k/sqrt(d)*log2(e) ~ ramp (+ noise)
+    q = (u * (d ** 0.5) / 1.44269504 + 0.3 * torch.randn(1, hq, n, d, generator=g)).to(dtype)
+    k = (ramp[None, None, :, None] * u + 0.3 * torch.randn(1, hkv, n, d, generator=g)).to(dtype)
+    v = _rand((1, hkv, n, d), 22, dtype)
+    if mode == "dense":
+        o, lse = sq.attn_causal(q.cuda(), k.cuda(), v.cuda(), "HND", dtype, True, False)
+        ro, rlse = so.dense_causal(q, k, v, output_dtype=dtype, return_lse=True)
+    else:
+        r = [0.5] * hq
+        o, lse = sq.attn_hierarchical_relative_window(q.cuda(), k.cuda(), q.cuda(), k.cuda(), v.cuda(), r, r, 128, "HND",
+                                                      dtype, True)
+        ro, rlse = so.windowed_prefill(q, k, q, k, v, r, r, 128, mode="relative", output_dtype=dtype, return_lse=True)
+    assert (rlse.max() - rlse.min()).item() > 40.0     # the maxima really span many octaves
+    _cmp(o, lse, ro, rlse)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("n,d,sink,r8,r4", [
     (1024, 128, 256, [0.1, 0.1, 0.1, 0.1], [0.1, 0.1, 0.1, 0.1]),   # the reference's effective default
