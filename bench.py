@@ -620,18 +620,38 @@ def run_decode_variants(args):
         g = torch.Generator(device=dev).manual_seed(5)
         qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16, generator=g)
 
+        ex = sqdist.PeerExchange(HQ, D) if (args.exchange == "peer" and world > 1) else None
+
         def step():
             for kk, vv in layers:
-                sqdist.sp_decode(qd, kk, vv, out_dtype=torch.bfloat16)
+                sqdist.sp_decode(qd, kk, vv, out_dtype=torch.bfloat16, exchange=ex)
 
         for _ in range(max(args.warmup, 3)):
             step()
         ms = timed(step, args.steps)
+        eager_ms = ms
+        if ex is not None:
+            # the whole step (28 x decode, split merge, step-counter advance, peer merge) replayed from a CUDA graph:
+            # no host work and no collective-library call between the layers
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            sync_all()
+            with torch.cuda.graph(graph):
+                step()
+            sync_all()
+            for _ in range(3):
+                graph.replay()
+            ms = timed(graph.replay, args.steps)
         nbytes = nl * 2.0 * HKV * n_total * D * 2
         res = {"workload": "decode_split_kv", "metric": "decode_attention_ms_per_token", "value": ms, "unit": "ms",
                "higher_is_better": False, "n_gpus": world, "context": n_total, "layers": nl,
-               "aggregate_gb_per_s": nbytes / (ms * 1e-3) / 1e9, "kv_gb_total": nbytes / 1e9, "steps": args.steps,
-               "parallelism": f"kv-shard x{world}", "data": "synthetic N(0,1) cache", "dtype": "bf16"}
+               "aggregate_gb_per_s": nbytes / (ms * 1e-3) / 1e9, "eager_ms": eager_ms,
+               "launch": "CUDA graph replay" if ex is not None else "eager", "kv_gb_total": nbytes / 1e9, "steps": args.steps,
+               "parallelism": f"kv-shard x{world}", "exchange": "peer stores in the merge kernel" if ex is not None else "nccl all-gather + merge kernel", "data": "synthetic N(0,1) cache", "dtype": "bf16"}
     elif args.workload == "decode_hybrid":
         n_total, nl = args.seq, args.layers
         cache = HybridKVCache(nl, 1, n_total, HKV, D, torch.bfloat16, gpu_fraction=0.25, device=dev)
@@ -696,6 +716,7 @@ def main():
     ap.add_argument("--seq", type=int, default=None, help="sequence length for --kernel-only / --workload")
     ap.add_argument("--workload", default="operator", choices=["operator", "ttft", "decode_model", "decode_sp", "decode_hybrid", "retrieval"],
                     help="operator: the headline line; ttft / decode_model: the operator inside the decoder stand-in")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="decode_sp: how the partials travel")
     ap.add_argument("--layers", type=int, default=28, help="decoder layers for --workload ttft / decode_model")
     args = ap.parse_args()
     if args.seq is None:

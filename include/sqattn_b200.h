@@ -236,6 +236,35 @@ int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t
                             int32_t seq_len, int32_t head_dim, int32_t relative, int32_t num_bins, int32_t sink,
                             double* hist, sqattn_stream_t stream);
 
+/* ---- cross-GPU merge of decode partials over peer memory (no counterpart in the reference, which has no
+ * multi-GPU attention path) ------------------------------------------------------------------------------- */
+
+/* One call per decode step on every rank.  `epoch` points to a device word, zero before the first call, that the
+ * call itself advances by one (so the same sequence of calls, captured in a CUDA graph, can be replayed); all
+ * ranks must have made the same number of calls.  Each rank passes its partial
+ * (part_o [rows, head_dim] fp32 already divided by its own sum, part_lse [rows] fp32 base 2, as produced by
+ * sqattn_decode with partial_o / partial_lse) and the device pointers of ALL ranks' exchange buffers as mapped
+ * in the calling process (symmetric / IPC memory; index = rank).  The kernel stores the partial into every
+ * rank's data buffer with plain peer stores, publishes a flag, waits at most one second for the other ranks
+ * (then SQATTN_ERR_DEVICE_TIMEOUT is reported by sqattn_check_device_status) and writes the merged result.
+ * Buffers: data = sqattn_peer_merge_data_bytes(), flags = sqattn_peer_merge_flag_bytes(), zeroed once before the
+ * first call.  At most 16 ranks. */
+typedef struct sqattn_peer_merge_args {
+  void* peer_data[16];
+  void* peer_flags[16];
+  int32_t rank, world;
+  int32_t rows, rows_cap, head_dim;
+  uint32_t* epoch;      /* device step counter, see above */
+  const float* part_o;
+  const float* part_lse;
+  void* out;            /* [rows, head_dim] in o_dtype */
+  int32_t o_dtype;
+  float* lse;           /* optional [rows] */
+} sqattn_peer_merge_args;
+size_t sqattn_peer_merge_data_bytes(int32_t world, int32_t rows_cap, int32_t head_dim);
+size_t sqattn_peer_merge_flag_bytes(int32_t world, int32_t rows_cap);
+int sqattn_decode_peer_merge(const sqattn_peer_merge_args* args, sqattn_stream_t stream);
+
 /* ---- decoder-layer row kernels: the caller's side of the operator (model_hub/utils.py) ------------------- */
 
 /* out[r, :] = (x[r, :] * rsqrt(mean(x[r, :]^2) + eps)) * weight, rmsnorm (model_hub/utils.py:14-18); 16-bit rows

@@ -71,6 +71,13 @@ class DecodeArgs(C.Structure):
 
 
 # every symbol include/sqattn_b200.h declares: (name, restype, argtypes)
+class PeerMergeArgs(C.Structure):
+    _fields_ = [("peer_data", C.c_void_p * 16), ("peer_flags", C.c_void_p * 16), ("rank", C.c_int32), ("world", C.c_int32),
+                ("rows", C.c_int32), ("rows_cap", C.c_int32), ("head_dim", C.c_int32), ("epoch", C.c_void_p),
+                ("part_o", C.c_void_p), ("part_lse", C.c_void_p), ("out", C.c_void_p), ("o_dtype", C.c_int32),
+                ("lse", C.c_void_p)]
+
+
 SYMBOLS = [
     ("sqattn_prefill_workspace_bytes", C.c_size_t, [C.POINTER(PrefillArgs)]),
     ("sqattn_prefill", C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
@@ -99,6 +106,9 @@ SYMBOLS = [
                                      C.c_int32, C.c_void_p, C.c_void_p]),
     ("sqattn_window_histogram", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                           C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    ("sqattn_peer_merge_data_bytes", C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    ("sqattn_peer_merge_flag_bytes", C.c_size_t, [C.c_int32, C.c_int32]),
+    ("sqattn_decode_peer_merge", C.c_int, [C.POINTER(PeerMergeArgs), C.c_void_p]),
     ("sqattn_rmsnorm", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_float,
                                  C.c_int32, C.c_void_p]),
     ("sqattn_rope_qk", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,

@@ -8,6 +8,7 @@
 #include "decode.cuh"
 #include "decoder_ops.cuh"
 #include "kmeans.cuh"
+#include "peer_exchange.cuh"
 #include "prefill.cuh"
 #include "prep.cuh"
 #include "retrieval.cuh"
@@ -690,6 +691,43 @@ int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32
   const int grid = elementwise_grid(rows * (inter / 8), 256);
   if (dtype == SQATTN_BF16) silu_mul_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), rows, inter);
   else silu_mul_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), rows, inter);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+// ---- cross-GPU merge over peer memory --------------------------------------------------------------------
+size_t sqattn_peer_merge_data_bytes(int32_t world, int32_t rows_cap, int32_t head_dim) {
+  if (world <= 0 || world > kPeerMaxWorld || rows_cap <= 0 || head_dim <= 0) return 0;
+  return static_cast<size_t>(2) * world * rows_cap * (head_dim + 1) * sizeof(float);
+}
+size_t sqattn_peer_merge_flag_bytes(int32_t world, int32_t rows_cap) {
+  if (world <= 0 || world > kPeerMaxWorld || rows_cap <= 0) return 0;
+  return static_cast<size_t>(world) * ((rows_cap + kPeerRowsPerCta - 1) / kPeerRowsPerCta) * sizeof(uint32_t);
+}
+
+int sqattn_decode_peer_merge(const sqattn_peer_merge_args* a, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!a) return fail(SQATTN_ERR_INVALID_ARG, "args is null");
+  if (a->world < 1 || a->world > kPeerMaxWorld || a->rank < 0 || a->rank >= a->world)
+    return fail(SQATTN_ERR_INVALID_ARG, "peer merge: rank %d of %d (at most %d ranks)", a->rank, a->world, kPeerMaxWorld);
+  if (a->rows <= 0 || a->rows > a->rows_cap || a->head_dim <= 0 || a->head_dim > 256)
+    return fail(SQATTN_ERR_INVALID_ARG, "peer merge: rows %d (capacity %d), head_dim %d", a->rows, a->rows_cap, a->head_dim);
+  if (!a->part_o || !a->part_lse || !a->out) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (!a->epoch) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: the device step counter is null");
+  PeerMergeParams p;
+  for (int w = 0; w < a->world; ++w) {
+    if (!a->peer_data[w] || !a->peer_flags[w]) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: buffer of rank %d is null", w);
+    p.data[w] = static_cast<float*>(a->peer_data[w]);
+    p.flags[w] = static_cast<uint32_t*>(a->peer_flags[w]);
+  }
+  p.part_o = a->part_o; p.part_lse = a->part_lse; p.out = a->out; p.lse = a->lse;
+  p.rank = a->rank; p.world = a->world; p.rows = a->rows; p.rows_cap = a->rows_cap; p.d = a->head_dim;
+  p.ctas_cap = (a->rows_cap + kPeerRowsPerCta - 1) / kPeerRowsPerCta;
+  p.o_dtype = a->o_dtype == SQATTN_BF16 ? 1 : 0;
+  p.epoch_ptr = a->epoch;
+  const int grid = (a->rows + kPeerRowsPerCta - 1) / kPeerRowsPerCta;
+  peer_epoch_advance_kernel<<<1, 1, 0, stream>>>(a->epoch);
+  peer_merge_kernel<<<grid, 128, 0, stream>>>(p);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }

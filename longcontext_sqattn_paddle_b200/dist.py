@@ -12,7 +12,10 @@ two places where the path shards naturally:
 * decode: the cache is sharded by key ranges; every rank computes (partial O, LSE) over its keys, one
   all-gather of [B*Hq, D+1] floats, one merge kernel.
 
-The collectives go through ``torch.distributed`` (NCCL on GPUs).  Kernels only ever read local memory.
+The collectives go through ``torch.distributed`` (NCCL on GPUs) and the attention kernels only ever read local
+memory.  For decode, where the exchange is 14 KB per rank and latency is everything, ``PeerExchange`` replaces
+the all-gather + merge by ONE kernel that stores the partials into every rank's buffer over NVLink (plain peer
+stores into symmetric memory), flags, waits and merges (csrc/peer_exchange.cuh).
 The compute steps are taken from a ``backend`` object so that the partitioning logic can be exercised on CPU
 ranks (gloo) with a stand-in backend; the default backend is the CUDA library and nothing else ships.
 """
@@ -22,6 +25,9 @@ from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist
+
+import ctypes as C
+import os
 
 from . import _lib as L
 
@@ -55,6 +61,56 @@ class CudaBackend:
     def merge(self, part_o, part_lse, out_dtype):
         from . import ops
         return ops.decode_merge(part_o, part_lse, out_dtype=out_dtype)
+
+
+class PeerExchange:
+    """Symmetric-memory buffers for the one-kernel cross-GPU merge (sqattn_decode_peer_merge).  Every rank
+    allocates the same two buffers, the ranks exchange mappings once (torch symmetric memory), and each decode
+    step is then a single kernel per rank with no NCCL call.  ``rows_cap`` = batch * query heads at most."""
+
+    def __init__(self, rows_cap: int, head_dim: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        if not dist.is_initialized():
+            raise RuntimeError("PeerExchange needs an initialised process group")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 16:
+            raise ValueError("PeerExchange supports at most 16 ranks")
+        self.rows_cap, self.d = int(rows_cap), int(head_dim)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        # plain peer loads/stores only: no NVLink multicast object is needed for this exchange
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        nd = L.lib.sqattn_peer_merge_data_bytes(self.world, self.rows_cap, self.d)
+        nf = L.lib.sqattn_peer_merge_flag_bytes(self.world, self.rows_cap)
+        self.data = symm_mem.empty(nd // 4, dtype=torch.float32, device=dev)
+        self.flags = symm_mem.empty(nf // 4, dtype=torch.int32, device=dev)
+        self.data.zero_()
+        self.flags.zero_()
+        self._hd = symm_mem.rendezvous(self.data, self.group)
+        self._hf = symm_mem.rendezvous(self.flags, self.group)
+        self.data_ptrs = [int(x) for x in self._hd.buffer_ptrs]
+        self.flag_ptrs = [int(x) for x in self._hf.buffer_ptrs]
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)   # everybody's buffers are zeroed before anybody's first store arrives
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)   # advanced on the device by every call
+
+    def merge(self, part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype=torch.bfloat16, return_lse: bool = False):
+        """part_o [rows, D] fp32, part_lse [rows] fp32 (this rank's partial) -> merged O [rows, D] on every rank."""
+        rows, d = part_o.shape
+        if d != self.d or rows > self.rows_cap:
+            raise ValueError(f"partial of shape {tuple(part_o.shape)} does not fit an exchange of {self.rows_cap} x {self.d}")
+        part_o, part_lse = part_o.contiguous(), part_lse.contiguous()
+        out = torch.empty(rows, d, dtype=out_dtype, device=part_o.device)
+        lse = torch.empty(rows, dtype=torch.float32, device=part_o.device) if return_lse else None
+        a = L.PeerMergeArgs()
+        for w in range(self.world):
+            a.peer_data[w], a.peer_flags[w] = self.data_ptrs[w], self.flag_ptrs[w]
+        a.rank, a.world, a.rows, a.rows_cap, a.head_dim, a.epoch = self.rank, self.world, rows, self.rows_cap, d, self.epoch.data_ptr()
+        a.part_o, a.part_lse, a.out = part_o.data_ptr(), part_lse.data_ptr(), out.data_ptr()
+        a.o_dtype = L.BF16 if out_dtype == torch.bfloat16 else L.F16
+        a.lse = None if lse is None else lse.data_ptr()
+        L.check(L.lib.sqattn_decode_peer_merge(C.byref(a), torch.cuda.current_stream().cuda_stream))
+        return (out, lse) if return_lse else out
 
 
 def shard_range(rank: int, world: int, seq_total: int):
@@ -116,14 +172,17 @@ def sp_prefill_wrapper(bit8_window_sizes, bit4_window_sizes, sink_window_size, a
 
 
 def sp_decode(q, k_shard, v_shard, *, kv_lens: Optional[Sequence[int]] = None, out_dtype=torch.bfloat16,
-              p_fp8: bool = False, group=None, backend=None):
+              p_fp8: bool = False, group=None, backend=None, exchange: Optional[PeerExchange] = None):
     """Split-KV decode across ranks.  q [B,Hq,1,D] (replicated), k_shard/v_shard [B,Hkv,Ls,D]: this rank's keys
-    (``kv_lens``: how many of them are valid per sequence).  Returns O [B,Hq,1,D] on every rank."""
+    (``kv_lens``: how many of them are valid per sequence).  Returns O [B,Hq,1,D] on every rank.  With
+    ``exchange`` the partials travel by peer stores inside one merge kernel instead of an NCCL all-gather."""
     backend = backend or CudaBackend()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     b, hq, _, d = q.shape
     po, pl = backend.decode_partial(q, k_shard, v_shard, kv_lens, p_fp8)  # [B,Hq,D] fp32, [B,Hq] fp32
     rows = b * hq
+    if exchange is not None:
+        return exchange.merge(po.reshape(rows, d), pl.reshape(rows), out_dtype).view(b, hq, 1, d)
     if world > 1:
         packed = torch.cat([po.reshape(rows, d), pl.reshape(rows, 1)], dim=1).contiguous()   # [rows, D+1]
         gathered = torch.empty(world, rows, d + 1, dtype=torch.float32, device=packed.device)

@@ -1,4 +1,4 @@
-"""Two-GPU run of the sequence-parallel prefill and the cross-GPU split-KV decode (NCCL).  Skipped on a
+"""Two-GPU run of the sequence-parallel prefill and the cross-GPU split-KV decode (NCCL and peer-store exchange).  Skipped on a
 single-GPU box; the partitioning logic itself is also covered by the gloo tests on CPU."""
 import os
 
@@ -45,6 +45,20 @@ def _worker(rank, world, port, tmp):
         torch.cuda.synchronize()
         ops.check_device_status()
         torch.save(od.cpu(), os.path.join(tmp, f"decode_{rank}.pt"))
+        # the same decode with the partials exchanged by peer stores inside one merge kernel; five steps with
+        # different queries so that both buffer parities and growing epochs are used
+        ex = sqdist.PeerExchange(rows_cap=b * hq, head_dim=d)
+        outs = []
+        for step in range(5):
+            qs = (qd.float() * (1.0 + 0.25 * step)).to(torch.bfloat16).cuda()
+            kk = kd[:, :, rank * ls:(rank + 1) * ls].contiguous().cuda()
+            vv = vd[:, :, rank * ls:(rank + 1) * ls].contiguous().cuda()
+            a = sqdist.sp_decode(qs, kk, vv, kv_lens=mine, exchange=ex)
+            n_ = sqdist.sp_decode(qs, kk, vv, kv_lens=mine)
+            outs.append((a.float() - n_.float()).abs().max().item())
+        torch.cuda.synchronize()
+        ops.check_device_status()
+        torch.save(torch.tensor(outs), os.path.join(tmp, f"peer_{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -66,3 +80,6 @@ def test_two_gpu_prefill_and_decode(tmp_path):
     refd = so.decode(qd, kd, vd, output_dtype=torch.bfloat16, center_k=False, kv_lens=[4096, 1500], mask_tail=True)
     for r in range(world):
         assert (torch.load(tmp_path / f"decode_{r}.pt").float() - refd.float()).abs().max().item() < 2e-2
+        # peer-store exchange against the NCCL exchange: the same partials merged in another order, so the
+        # difference is at most one unit in the last place of the 16-bit output
+        assert torch.load(tmp_path / f"peer_{r}.pt").max().item() < 8e-3
