@@ -177,7 +177,9 @@ def _both(gen):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python make_golden.py <path to a checkout of the reference repository>")
+    ref_root = sys.argv[1]
     _stub_modules(ref_root)
     _repair_interpreter_fp8()
     cases = {
