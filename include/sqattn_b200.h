@@ -151,6 +151,10 @@ typedef struct {
    * (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of THIS call's keys is written there for sqattn_decode_merge */
   float* partial_o;
   float* partial_lse;
+  /* Lengths that live on the device (int32 [B]), for callers that replay a captured CUDA graph while the cache
+   * grows: the key ranges are planned on the host for kv_len (the capacity to plan for, kv_lens must be NULL) and
+   * the kernel clips every range to the length it reads from this array; ranges past the end contribute nothing. */
+  const int32_t* kv_lens_device;
 } sqattn_decode_args;
 
 /* Replaces attn_unified's decode branch + _attn_decode_fwd, sqattn/attn_triton_decode.py:175-241,
@@ -276,6 +280,11 @@ int sqattn_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, i
  * cos|sin = cos_sin_cache[pos0 + row % seq_len] (fp32 [cache_rows, head_dim]). */
 int sqattn_rope_qk(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads, int32_t head_dim,
                    const float* cos_sin_cache, int64_t cache_rows, int64_t pos0, int32_t dtype, sqattn_stream_t stream);
+/* The same with the first position read from a device word (int64) at run time, added to pos0: for callers that
+ * replay a captured graph while the position advances.  Positions past the table are clamped to its last row. */
+int sqattn_rope_qk_devpos(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads,
+                          int32_t head_dim, const float* cos_sin_cache, int64_t cache_rows, int64_t pos0,
+                          const int64_t* pos_device, int32_t dtype, sqattn_stream_t stream);
 /* silu_and_mul (model_hub/utils.py:4-12): x [rows, 2*inter] -> out [rows, inter] = x[:, inter:] * silu(x[:, :inter]) */
 int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32_t dtype, sqattn_stream_t stream);
 

@@ -66,7 +66,7 @@ class DecodeArgs(C.Structure):
         ("dtype", C.c_int32), ("o_dtype", C.c_int32), ("p_fp8", C.c_int32), ("q_is_scaled", C.c_int32),
         ("num_splits", C.c_int32), ("reference_tail", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("kv_lens_device", C.c_void_p),
     ]
 
 
@@ -113,6 +113,8 @@ SYMBOLS = [
                                  C.c_int32, C.c_void_p]),
     ("sqattn_rope_qk", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
                                  C.c_int64, C.c_int32, C.c_void_p]),
+    ("sqattn_rope_qk_devpos", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                        C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p]),
     ("sqattn_silu_mul", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]),
     ("sqattn_cache_copy_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
                                          C.c_void_p]),

@@ -30,6 +30,7 @@ struct DecodeParams {
   int reference_tail;  // keys between a sequence's length and the next multiple of 64 count with score 0
   float sm_scale;  // 1/sqrt(D) * 1.44269504 evaluated in double on the host, like the Python launcher
   int lens[kDecMaxBatch];
+  const int* lens_dev;  // when set, the lengths are read from the device at run time (lens[] holds the planned capacity)
   int item_prefix[kDecMaxBatch + 1];  // first work item of each sequence
 };
 
@@ -100,7 +101,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (p.item_prefix[mid] <= item) lo = mid; else hi = mid;
   }
   const int bi = lo;
-  const int len = p.lens[bi];
+  const int len = p.lens_dev ? min(p.lens_dev[bi], p.lens[bi]) : p.lens[bi];
   const int key_begin = (item - p.item_prefix[bi]) * p.chunk;
   const int key_end = min(len, key_begin + p.chunk);  // real keys
   // The reference kernel loads keys past kv_len as zeros without masking their scores (masked tl.load,

@@ -61,7 +61,9 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint8_t* __restrict_
 template <bool BF16>
 __global__ void __launch_bounds__(256) rope_kernel(uint8_t* __restrict__ qkv, long long row_stride, long long rows,
                                                    int seq_len, int heads, int head_dim,
-                                                   const float* __restrict__ cache, long long pos0) {
+                                                   const float* __restrict__ cache, long long pos0,
+                                                   const long long* __restrict__ pos_dev, long long cache_rows) {
+  if (pos_dev) pos0 += *pos_dev;
   const int half = head_dim / 2, vec_per_head = half / 8;
   const long long total = rows * heads * vec_per_head;
   for (long long idx = blockIdx.x * 256ll + threadIdx.x; idx < total; idx += 256ll * gridDim.x) {
@@ -69,7 +71,8 @@ __global__ void __launch_bounds__(256) rope_kernel(uint8_t* __restrict__ qkv, lo
     const long long rh = idx / vec_per_head;
     const int h = static_cast<int>(rh % heads);
     const long long row = rh / heads;
-    const long long pos = pos0 + row % seq_len;
+    long long pos = pos0 + row % seq_len;
+    if (pos >= cache_rows) pos = cache_rows - 1;
     uint8_t* base = qkv + 2 * (row * row_stride + static_cast<long long>(h) * head_dim + v * 8);
     const float4* cs = reinterpret_cast<const float4*>(cache + pos * head_dim + v * 8);
     const float4* sn = reinterpret_cast<const float4*>(cache + pos * head_dim + half + v * 8);

@@ -205,6 +205,7 @@ int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
   if (a->batch <= 0 || a->batch > kDecMaxBatch) return fail(SQATTN_ERR_UNSUPPORTED, "batch must be in [1, %d]", kDecMaxBatch);
   if (a->num_kv_heads <= 0 || a->num_q_heads % a->num_kv_heads) return fail(SQATTN_ERR_INVALID_ARG, "bad head counts");
   if (a->num_q_heads / a->num_kv_heads > 16) return fail(SQATTN_ERR_UNSUPPORTED, "more than 16 query heads per KV head");
+  if (a->kv_lens_device && a->kv_lens) return fail(SQATTN_ERR_INVALID_ARG, "kv_lens and kv_lens_device are exclusive: device lengths are planned for kv_len");
   long long total_tiles = 0;
   for (int b = 0; b < a->batch; ++b) {
     const int len = a->kv_lens ? a->kv_lens[b] : a->kv_len;
@@ -260,6 +261,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   p.chunk = pl.chunk; p.p_fp8 = a->p_fp8; p.q_is_scaled = a->q_is_scaled; p.reference_tail = a->reference_tail;
   p.sm_scale = static_cast<float>(sm_scale_log2(D));
   memcpy(p.lens, pl.lens, sizeof(int) * a->batch);
+  p.lens_dev = a->kv_lens_device;
   memcpy(p.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
   using L = DecodeSmem<D>;
   static bool attr_set = false;
@@ -665,23 +667,31 @@ int sqattn_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, i
   return SQATTN_OK;
 }
 
-int sqattn_rope_qk(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads, int32_t head_dim,
-                   const float* cos_sin_cache, int64_t cache_rows, int64_t pos0, int32_t dtype, sqattn_stream_t stream_) {
+int sqattn_rope_qk_devpos(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads,
+                          int32_t head_dim, const float* cos_sin_cache, int64_t cache_rows, int64_t pos0,
+                          const int64_t* pos_device, int32_t dtype, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!qkv || !cos_sin_cache) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
   if (head_dim <= 0 || head_dim % 16) return fail(SQATTN_ERR_UNSUPPORTED, "rope: head_dim %d must be a multiple of 16", head_dim);
   if (rows <= 0 || seq_len <= 0 || num_heads <= 0 || row_stride % 8 || row_stride < static_cast<int64_t>(num_heads) * head_dim)
     return fail(SQATTN_ERR_INVALID_ARG, "rope: bad sizes");
-  if (pos0 < 0 || pos0 + seq_len > cache_rows)
+  if (pos0 < 0 || (!pos_device && pos0 + seq_len > cache_rows))
     return fail(SQATTN_ERR_INVALID_ARG, "rope: positions %lld..%lld exceed the cos/sin cache (%lld rows)",
                 static_cast<long long>(pos0), static_cast<long long>(pos0 + seq_len), static_cast<long long>(cache_rows));
   const int grid = elementwise_grid(rows * num_heads * (head_dim / 16), 256);
+  const long long* pd = reinterpret_cast<const long long*>(pos_device);
   if (dtype == SQATTN_BF16)
-    rope_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(qkv), row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, pos0);
+    rope_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(qkv), row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, pos0, pd, cache_rows);
   else
-    rope_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(qkv), row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, pos0);
+    rope_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(qkv), row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, pos0, pd, cache_rows);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
+}
+
+int sqattn_rope_qk(void* qkv, int64_t row_stride, int64_t rows, int32_t seq_len, int32_t num_heads, int32_t head_dim,
+                   const float* cos_sin_cache, int64_t cache_rows, int64_t pos0, int32_t dtype, sqattn_stream_t stream_) {
+  return sqattn_rope_qk_devpos(qkv, row_stride, rows, seq_len, num_heads, head_dim, cos_sin_cache, cache_rows, pos0,
+                               nullptr, dtype, stream_);
 }
 
 int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32_t dtype, sqattn_stream_t stream_) {

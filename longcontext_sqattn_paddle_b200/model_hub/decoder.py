@@ -108,13 +108,15 @@ class DecoderLayer:
         out = K.attn_causal(query_states, key_states, value_states, tensor_layout="NHD", output_dtype=query_states.dtype)
         return out.reshape(b, n, hq * d)
 
-    def decode_attention(self, query_states, key_states, value_states, layer_idx=None, kv_lens=None):
+    def decode_attention(self, query_states, key_states, value_states, layer_idx=None, kv_lens=None,
+                         kv_lens_device=None):
         """One query token per sequence against the layer's cache [B,capacity,Hkv,D] (model_hub/qwen.py:50-56);
-        ``kv_lens`` are the valid lengths (the reference attends to the whole allocation)."""
+        ``kv_lens`` are the valid lengths (the reference attends to the whole allocation), on the host or, for a
+        captured step, on the device."""
         if self.attention_type not in ("SQAttn", "SDPA", "FlashAttn"):
             raise ValueError(f"Unsupported attention type: {self.attention_type}")
         return ops.decode(query_states, key_states, value_states, layout="NHD", out_dtype=query_states.dtype,
-                          kv_lens=kv_lens)
+                          kv_lens=kv_lens, kv_lens_device=kv_lens_device)
 
 
 class RandomInitDecoder:
@@ -165,11 +167,13 @@ class RandomInitDecoder:
         q, k, v = qkv.split([self.hidden_size, kv, kv], dim=-1)
         return qkv, q, k, v
 
-    def position_embedd(self, qkv, seq_len, shard_offset=0):
-        """Rotate the query and key heads of the fused buffer in place at positions context + shard_offset + t."""
+    def position_embedd(self, qkv, seq_len, shard_offset=0, pos_device=None):
+        """Rotate the query and key heads of the fused buffer in place at positions context + shard_offset + t
+        (the context read from ``pos_device`` when a captured step is replayed)."""
         b = qkv.shape[0]
+        pos0 = shard_offset if pos_device is not None else self.kv_cache.context + shard_offset
         ops.rope_qk(qkv.view(b * seq_len, qkv.shape[-1]), seq_len, self.num_heads + self.num_key_value_heads,
-                    self.head_dim, self.cos_sin_cache, self.kv_cache.context + shard_offset)
+                    self.head_dim, self.cos_sin_cache, pos0, pos_device=pos_device)
 
     def wo(self, hidden_states, layer, bsz, seq_len, dim):
         return F.linear(hidden_states.reshape(bsz, seq_len, dim), layer.wo)
@@ -204,19 +208,21 @@ class RandomInitDecoder:
             chunk += self.mlp(normed, layer)
         return hidden_states
 
-    def layer_decode(self, layer_idx, hidden_states):
+    def layer_decode(self, layer_idx, hidden_states, dev=None):
+        """``dev`` = (position int64 [1], lengths int32 [B]) on the GPU when the step is being captured for replay."""
         residual = hidden_states
         bsz, seq_len, dim = hidden_states.shape
         layer = self.layers[layer_idx]
         normed = self.layernorm(hidden_states, layer.input_layernorm_variance_epsilon, layer.input_layernorm_weight)
         qkv, q, k, v = self.wqkv(normed, layer)
-        self.position_embedd(qkv, seq_len)
+        self.position_embedd(qkv, seq_len, pos_device=None if dev is None else dev[0])
         query_states = q.view(bsz, seq_len, self.num_heads, self.head_dim)
         key_states = k.view(bsz, seq_len, self.num_key_value_heads, self.head_dim)
         value_states = v.view(bsz, seq_len, self.num_key_value_heads, self.head_dim)
-        lens = [x + 1 for x in self.kv_cache.valid_length_host]
+        lens = None if dev is not None else [x + 1 for x in self.kv_cache.valid_length_host]
         key_states, value_states = self.kv_cache.decode_update_kv_cache(key_states, value_states, layer_idx)
-        attn_out = layer.decode_attention(query_states, key_states, value_states, None, kv_lens=lens)
+        attn_out = layer.decode_attention(query_states, key_states, value_states, None, kv_lens=lens,
+                                          kv_lens_device=None if dev is None else dev[1])
         hidden_states = residual + self.wo(attn_out, layer, bsz, seq_len, dim)
         residual = hidden_states
         normed = self.layernorm(hidden_states, layer.post_attention_layernorm_variance_epsilon,
@@ -236,12 +242,64 @@ class RandomInitDecoder:
         last_hidden_states = self.layernorm(last_hidden_states.contiguous(), self.norm_variance_epsilon, self.norm_weight)
         return self.lm(last_hidden_states)
 
-    def decode_forward(self, inputs_ids):
+    def decode_forward(self, inputs_ids, dev=None):
         hidden_states = self.word_embedding(inputs_ids)
         for ldx in range(self.num_layers):
-            hidden_states = self.layer_decode(ldx, hidden_states)
+            hidden_states = self.layer_decode(ldx, hidden_states, dev)
         hidden_states = self.layernorm(hidden_states[:, -1:, :].contiguous(), self.norm_variance_epsilon, self.norm_weight)
         return self.lm(hidden_states)
+
+    # ---- one decode step as a replayable CUDA graph ---------------------------------------------------
+    def _host_state(self):
+        kc = self.kv_cache
+        return kc.context, list(kc.valid_length_host)
+
+    def _set_host_state(self, st):
+        self.kv_cache.context, self.kv_cache.valid_length_host = st[0], list(st[1])
+
+    def capture_decode_step(self, batch_size: int):
+        """Capture ``decode_forward`` for replay: everything that changes from token to token (position, cache
+        lengths, the index the new key/value rows go to) lives on the GPU and is advanced inside the graph, so
+        ``decode_forward_graph`` is one graph launch per token with no host work between the layers."""
+        kc = self.kv_cache
+        if kc is None or kc.valid_length is None or not kc.allocated:
+            raise RuntimeError("capture_decode_step needs a prefilled, GPU-resident cache")
+        dev = self.device
+        self._g_ids = torch.zeros(batch_size, 1, dtype=torch.int64, device=dev)
+        self._g_pos = torch.full((1,), kc.context, dtype=torch.int64, device=dev)
+        self._g_lens = torch.zeros(batch_size, dtype=torch.int32, device=dev)
+
+        def step():
+            self._g_lens.copy_((kc.valid_length + 1).to(torch.int32))
+            logits = self.decode_forward(self._g_ids, dev=(self._g_pos, self._g_lens))   # advances valid_length
+            self._g_pos += 1
+            return logits
+
+        # warm-up outside capture (library workspaces, lazy initialisation), then put the state back: the rows it
+        # wrote at index valid_length are overwritten by the first real step
+        host, vl = self._host_state(), kc.valid_length.clone()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        kc.valid_length.copy_(vl)
+        self._g_pos.fill_(host[0])
+        self._set_host_state(host)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._g_logits = step()
+        self._set_host_state(host)   # capture ran the Python bookkeeping once without running any kernel
+
+    def decode_forward_graph(self, inputs_ids):
+        """``decode_forward`` through the captured graph; returns a view of the graph's logits buffer."""
+        self._g_ids.copy_(inputs_ids)
+        self._graph.replay()
+        kc = self.kv_cache
+        kc.context += 1
+        kc.valid_length_host = [x + 1 for x in kc.valid_length_host]
+        return self._g_logits
 
     # ---- generation (model_hub/LLM.py:160-235, model_hub/qwen.py:269-290) ------------------------------
     def init_kv_cache(self, real_input_length, valid_start):

@@ -161,10 +161,13 @@ def k_column_sums(key: torch.Tensor) -> torch.Tensor:
 
 def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse: bool = False, p_fp8: bool = False,
            q_is_scaled: bool = False, kv_lens: Optional[Sequence[int]] = None, kv_len: Optional[int] = None,
-           num_splits: int = 0, partial: bool = False, reference_tail: bool = False):
+           num_splits: int = 0, partial: bool = False, reference_tail: bool = False,
+           kv_lens_device: Optional[torch.Tensor] = None):
     """sqattn_decode.  q [B,Hq,1,D] (HND) or [B,1,Hq,D] (NHD); k/v caches of capacity >= kv_len.
     partial=True returns (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of these keys for a later merge.
-    reference_tail=True reproduces the reference kernel's zero-score padding of the last 64-key tile."""
+    reference_tail=True reproduces the reference kernel's zero-score padding of the last 64-key tile.
+    kv_lens_device (int32 [B] on the GPU): the lengths are read by the kernel at run time and ``kv_len`` is only the
+    capacity the key ranges are planned for, so the call can sit in a CUDA graph that is replayed as the cache grows."""
     _require_cuda(q, k, v)
     b, hq, one, d = _shape(q, layout)
     assert one == 1
@@ -179,6 +182,11 @@ def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse:
         a.kv_lens = lens
     a.dtype, a.p_fp8, a.q_is_scaled, a.num_splits = _dt(k.dtype), int(p_fp8), int(q_is_scaled), int(num_splits)
     a.reference_tail = int(reference_tail)
+    if kv_lens_device is not None:
+        if kv_lens is not None:
+            raise ValueError("kv_lens and kv_lens_device are exclusive: device lengths are planned for kv_len")
+        assert kv_lens_device.is_cuda and kv_lens_device.dtype == torch.int32 and kv_lens_device.numel() == b
+        a.kv_lens_device = kv_lens_device.data_ptr()
     out = lse = po = pl = None
     if partial:
         po = torch.empty(b, hq, d, dtype=torch.float32, device=q.device)
@@ -261,14 +269,19 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[tor
     return out
 
 
-def rope_qk(qkv: torch.Tensor, seq_len: int, num_heads: int, head_dim: int, cos_sin_cache: torch.Tensor, pos0: int):
+def rope_qk(qkv: torch.Tensor, seq_len: int, num_heads: int, head_dim: int, cos_sin_cache: torch.Tensor, pos0: int,
+            pos_device: Optional[torch.Tensor] = None):
     """sqattn_rope_qk: rotate the first num_heads heads of every row of the fused projection qkv [rows, width]
-    in place; row r takes position pos0 + r % seq_len of cos_sin_cache [max_len, head_dim] (fp32)."""
+    in place; row r takes position pos0 + r % seq_len of cos_sin_cache [max_len, head_dim] (fp32).  With
+    ``pos_device`` (int64 [1] on the GPU) that value is added to pos0 when the kernel runs."""
     _require_cuda(qkv, cos_sin_cache)
     assert qkv.dim() == 2 and qkv.stride(1) == 1
     assert cos_sin_cache.dtype == torch.float32 and cos_sin_cache.is_contiguous() and cos_sin_cache.shape[1] == head_dim
-    L.check(L.lib.sqattn_rope_qk(qkv.data_ptr(), qkv.stride(0), qkv.shape[0], int(seq_len), int(num_heads), int(head_dim),
-                                 cos_sin_cache.data_ptr(), cos_sin_cache.shape[0], int(pos0), _dt(qkv.dtype), _stream()))
+    if pos_device is not None:
+        assert pos_device.is_cuda and pos_device.dtype == torch.int64
+    L.check(L.lib.sqattn_rope_qk_devpos(qkv.data_ptr(), qkv.stride(0), qkv.shape[0], int(seq_len), int(num_heads),
+                                        int(head_dim), cos_sin_cache.data_ptr(), cos_sin_cache.shape[0], int(pos0),
+                                        None if pos_device is None else pos_device.data_ptr(), _dt(qkv.dtype), _stream()))
     return qkv
 
 

@@ -190,3 +190,63 @@ def test_generate_decode_steps_against_oracle():
     got = model2.decode_forward(tok.cuda()).cpu()
     scale = ref.abs().max().item()
     assert (got - ref).abs().max().item() < 0.05 * scale
+
+
+@pytest.mark.gpu
+def test_rope_with_device_position_matches_host_position():
+    from longcontext_sqattn_paddle_b200 import ops
+    from longcontext_sqattn_paddle_b200.model_hub import yarn_cos_sin_cache
+    torch.manual_seed(4)
+    table, _ = yarn_cos_sin_cache(128, 1e6, 5000, 32768)
+    table = table.cuda()
+    x = torch.randn(3, 6 * 128).to(torch.bfloat16).cuda()
+    a, b = x.clone(), x.clone()
+    ops.rope_qk(a, 1, 4, 128, table, 777)
+    ops.rope_qk(b, 1, 4, 128, table, 0, pos_device=torch.tensor([777], dtype=torch.int64, device="cuda"))
+    assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+def test_decode_with_device_lengths_matches_host_lengths():
+    from longcontext_sqattn_paddle_b200 import ops
+    torch.manual_seed(6)
+    b, hq, hkv, cap, d = 3, 8, 2, 5000, 128
+    q = torch.randn(b, 1, hq, d).to(torch.bfloat16).cuda()
+    k = torch.randn(b, cap, hkv, d).to(torch.bfloat16).cuda()
+    v = torch.randn(b, cap, hkv, d).to(torch.bfloat16).cuda()
+    lens = [4999, 130, 2048]
+    ref = ops.decode(q, k, v, layout="NHD", out_dtype=torch.bfloat16, kv_lens=lens)
+    dev = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    got = ops.decode(q, k, v, layout="NHD", out_dtype=torch.bfloat16, kv_len=cap, kv_lens_device=dev)
+    # the key ranges are planned for the capacity instead of the lengths: other split points, same attention
+    assert (got.float() - ref.float()).abs().max().item() < 8e-3
+    with pytest.raises(ValueError):
+        ops.decode(q, k, v, layout="NHD", kv_lens=lens, kv_lens_device=dev)
+
+
+@pytest.mark.gpu
+def test_captured_decode_step_follows_the_eager_one():
+    n, new = 300, 6
+    g = torch.Generator().manual_seed(13)
+    eager, graphed = _small_model(layers=2, seed=3), _small_model(layers=2, seed=3)
+    ids = torch.randint(0, eager.vocab_size, (1, n), generator=g).cuda()
+    for m in (eager, graphed):
+        m.batch_size, m.max_new_length = 1, new + 2
+        m.init_kv_cache(n, (0,))
+        m.prefill_forward(ids)
+        m.move()
+    graphed.capture_decode_step(1)
+    tok = torch.tensor([[5]], device="cuda")
+    for step in range(new):
+        le = eager.decode_forward(tok)
+        lg = graphed.decode_forward_graph(tok)
+        scale = le.abs().max().item()
+        assert (le - lg).abs().max().item() < 0.03 * scale, f"step {step}"
+        tok = le.argmax(dim=-1)
+    torch.cuda.synchronize()
+    assert graphed.kv_cache.context == eager.kv_cache.context == n + new
+    assert graphed.kv_cache.valid_length_host == eager.kv_cache.valid_length_host
+    assert torch.equal(graphed.kv_cache.valid_length, eager.kv_cache.valid_length)
+    # the caches hold the same rows: the graph wrote each new key where the eager step did
+    ke, kg = eager.kv_cache.key_cache[1][0, :n + new].float(), graphed.kv_cache.key_cache[1][0, :n + new].float()
+    assert (ke - kg).abs().max().item() < 0.05
