@@ -131,6 +131,8 @@ int sqattn_k_column_sums(const sqattn_tensor* k, int32_t batch, int32_t num_kv_h
 
 /* ---- decode ------------------------------------------------------------------------------- */
 
+struct sqattn_peer_merge_args;
+
 typedef struct {
   sqattn_tensor q;         /* [B, Hq, 1, D] */
   sqattn_tensor k, v;      /* [B, Hkv, kv_capacity, D] */
@@ -155,6 +157,10 @@ typedef struct {
    * grows: the key ranges are planned on the host for kv_len (the capacity to plan for, kv_lens must be NULL) and
    * the kernel clips every range to the length it reads from this array; ranges past the end contribute nothing. */
   const int32_t* kv_lens_device;
+  /* Cross-GPU split-KV in one step: when set, the kernel that merges this call's split-KV partials also exchanges
+   * them with the other ranks and merges across ranks (see sqattn_decode_peer_merge; its part_o / part_lse are
+   * ignored, its out / lse receive the result; o, lse, partial_o and partial_lse of this struct are not used). */
+  const struct sqattn_peer_merge_args* peer;
 } sqattn_decode_args;
 
 /* Replaces attn_unified's decode branch + _attn_decode_fwd, sqattn/attn_triton_decode.py:175-241,
@@ -244,7 +250,7 @@ int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t
  * multi-GPU attention path) ------------------------------------------------------------------------------- */
 
 /* One call per decode step on every rank.  `epoch` points to a device word, zero before the first call, that the
- * call itself advances by one (so the same sequence of calls, captured in a CUDA graph, can be replayed); all
+ * kernel itself advances by one (so the same sequence of calls, captured in a CUDA graph, can be replayed); all
  * ranks must have made the same number of calls.  Each rank passes its partial
  * (part_o [rows, head_dim] fp32 already divided by its own sum, part_lse [rows] fp32 base 2, as produced by
  * sqattn_decode with partial_o / partial_lse) and the device pointers of ALL ranks' exchange buffers as mapped

@@ -66,7 +66,7 @@ class DecodeArgs(C.Structure):
         ("dtype", C.c_int32), ("o_dtype", C.c_int32), ("p_fp8", C.c_int32), ("q_is_scaled", C.c_int32),
         ("num_splits", C.c_int32), ("reference_tail", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("kv_lens_device", C.c_void_p),
+        ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("kv_lens_device", C.c_void_p), ("peer", C.c_void_p),
     ]
 
 

@@ -241,6 +241,28 @@ size_t decode_ws_bytes(const sqattn_decode_args* a, const DecodePlan& pl) {
   return align_up(rows * a->head_dim * 4, 256) + align_up(rows * 4, 256);
 }
 
+// ---- cross-GPU merge over peer memory --------------------------------------------------------------------
+int fill_peer_params(const sqattn_peer_merge_args* a, PeerMergeParams* p) {
+  if (a->world < 1 || a->world > kPeerMaxWorld || a->rank < 0 || a->rank >= a->world)
+    return fail(SQATTN_ERR_INVALID_ARG, "peer merge: rank %d of %d (at most %d ranks)", a->rank, a->world, kPeerMaxWorld);
+  if (a->rows <= 0 || a->rows > a->rows_cap || a->head_dim <= 0 || a->head_dim > 128)
+    return fail(SQATTN_ERR_INVALID_ARG, "peer merge: rows %d (capacity %d), head_dim %d", a->rows, a->rows_cap, a->head_dim);
+  if (!a->out) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: null output pointer");
+  if (!a->epoch) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: the device step counter is null");
+  memset(p, 0, sizeof(*p));
+  for (int w = 0; w < a->world; ++w) {
+    if (!a->peer_data[w] || !a->peer_flags[w]) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: buffer of rank %d is null", w);
+    p->data[w] = static_cast<float*>(a->peer_data[w]);
+    p->flags[w] = static_cast<uint32_t*>(a->peer_flags[w]);
+  }
+  p->out = a->out; p->lse = a->lse;
+  p->rank = a->rank; p->world = a->world; p->rows = a->rows; p->rows_cap = a->rows_cap; p->d = a->head_dim;
+  p->o_dtype = a->o_dtype == SQATTN_BF16 ? 1 : 0;
+  p->epoch_ptr = a->epoch;
+  p->done = p->flags[a->rank] + static_cast<size_t>(a->world) * a->rows_cap;  // the word behind this rank's flags
+  return SQATTN_OK;
+}
+
 template <int D, bool BF16>
 int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_t stream) {
   CUtensorMap tk, tv;
@@ -275,6 +297,19 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
     SQ_CUDA(cudaGetLastError());
   }
 
+  if (a->peer) {
+    // the split-KV merge, the exchange with the other GPUs and the merge across GPUs in one kernel
+    PeerMergeParams pm;
+    if ((rc = fill_peer_params(a->peer, &pm))) return rc;
+    if (a->peer->rows != a->batch * a->num_q_heads || a->peer->head_dim != D)
+      return fail(SQATTN_ERR_INVALID_ARG, "peer merge: %d rows x %d expected, exchange describes %d x %d",
+                  a->batch * a->num_q_heads, D, a->peer->rows, a->peer->head_dim);
+    pm.part_o = p.part_o; pm.part_lse = p.part_lse; pm.split_mode = 1; pm.hq = a->num_q_heads;
+    memcpy(pm.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
+    peer_merge_kernel<<<static_cast<unsigned>(pm.rows), 128 * kMergeGroups, 0, stream>>>(pm);
+    SQ_CUDA(cudaGetLastError());
+    return SQATTN_OK;
+  }
   MergeParams m;
   memset(&m, 0, sizeof(m));
   m.part_o = p.part_o; m.part_lse = p.part_lse;
@@ -417,7 +452,7 @@ int sqattn_decode(const sqattn_decode_args* a, sqattn_stream_t stream_) {
   int rc = plan_decode(a, &pl);
   if (rc) return rc;
   if (!a->q.ptr || !a->k.ptr || !a->v.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
-  if (!a->partial_o && !a->o.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null output pointer");
+  if (!a->partial_o && !a->o.ptr && !a->peer) return fail(SQATTN_ERR_INVALID_ARG, "null output pointer");
   if (a->partial_o && !a->partial_lse) return fail(SQATTN_ERR_INVALID_ARG, "partial_lse missing");
   if (!aligned16(a->k) || !aligned16(a->v)) return fail(SQATTN_ERR_INVALID_ARG, "k/v need 16-byte alignment");
   if ((reinterpret_cast<uintptr_t>(a->q.ptr) % 4) || (a->q.stride_h % 2) || (a->q.stride_b % 2)) return fail(SQATTN_ERR_INVALID_ARG, "q needs 4-byte alignment");
@@ -705,39 +740,24 @@ int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32
   return SQATTN_OK;
 }
 
-// ---- cross-GPU merge over peer memory --------------------------------------------------------------------
 size_t sqattn_peer_merge_data_bytes(int32_t world, int32_t rows_cap, int32_t head_dim) {
   if (world <= 0 || world > kPeerMaxWorld || rows_cap <= 0 || head_dim <= 0) return 0;
   return static_cast<size_t>(2) * world * rows_cap * (head_dim + 1) * sizeof(float);
 }
 size_t sqattn_peer_merge_flag_bytes(int32_t world, int32_t rows_cap) {
   if (world <= 0 || world > kPeerMaxWorld || rows_cap <= 0) return 0;
-  return static_cast<size_t>(world) * ((rows_cap + kPeerRowsPerCta - 1) / kPeerRowsPerCta) * sizeof(uint32_t);
+  return (static_cast<size_t>(world) * rows_cap + 4) * sizeof(uint32_t);
 }
 
 int sqattn_decode_peer_merge(const sqattn_peer_merge_args* a, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!a) return fail(SQATTN_ERR_INVALID_ARG, "args is null");
-  if (a->world < 1 || a->world > kPeerMaxWorld || a->rank < 0 || a->rank >= a->world)
-    return fail(SQATTN_ERR_INVALID_ARG, "peer merge: rank %d of %d (at most %d ranks)", a->rank, a->world, kPeerMaxWorld);
-  if (a->rows <= 0 || a->rows > a->rows_cap || a->head_dim <= 0 || a->head_dim > 256)
-    return fail(SQATTN_ERR_INVALID_ARG, "peer merge: rows %d (capacity %d), head_dim %d", a->rows, a->rows_cap, a->head_dim);
-  if (!a->part_o || !a->part_lse || !a->out) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
-  if (!a->epoch) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: the device step counter is null");
+  if (!a->part_o || !a->part_lse) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
   PeerMergeParams p;
-  for (int w = 0; w < a->world; ++w) {
-    if (!a->peer_data[w] || !a->peer_flags[w]) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: buffer of rank %d is null", w);
-    p.data[w] = static_cast<float*>(a->peer_data[w]);
-    p.flags[w] = static_cast<uint32_t*>(a->peer_flags[w]);
-  }
-  p.part_o = a->part_o; p.part_lse = a->part_lse; p.out = a->out; p.lse = a->lse;
-  p.rank = a->rank; p.world = a->world; p.rows = a->rows; p.rows_cap = a->rows_cap; p.d = a->head_dim;
-  p.ctas_cap = (a->rows_cap + kPeerRowsPerCta - 1) / kPeerRowsPerCta;
-  p.o_dtype = a->o_dtype == SQATTN_BF16 ? 1 : 0;
-  p.epoch_ptr = a->epoch;
-  const int grid = (a->rows + kPeerRowsPerCta - 1) / kPeerRowsPerCta;
-  peer_epoch_advance_kernel<<<1, 1, 0, stream>>>(a->epoch);
-  peer_merge_kernel<<<grid, 128, 0, stream>>>(p);
+  int rc = fill_peer_params(a, &p);
+  if (rc) return rc;
+  p.part_o = a->part_o; p.part_lse = a->part_lse; p.split_mode = 0; p.hq = 1;
+  peer_merge_kernel<<<static_cast<unsigned>(p.rows), 128 * kMergeGroups, 0, stream>>>(p);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }

@@ -94,6 +94,16 @@ class PeerExchange:
         dist.barrier(self.group)   # everybody's buffers are zeroed before anybody's first store arrives
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)   # advanced on the device by every call
 
+    def _args(self, rows: int, out: torch.Tensor, lse: Optional[torch.Tensor]):
+        a = L.PeerMergeArgs()
+        for w in range(self.world):
+            a.peer_data[w], a.peer_flags[w] = self.data_ptrs[w], self.flag_ptrs[w]
+        a.rank, a.world, a.rows, a.rows_cap, a.head_dim, a.epoch = self.rank, self.world, rows, self.rows_cap, self.d, self.epoch.data_ptr()
+        a.out = out.data_ptr()
+        a.o_dtype = L.BF16 if out.dtype == torch.bfloat16 else L.F16
+        a.lse = None if lse is None else lse.data_ptr()
+        return a
+
     def merge(self, part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype=torch.bfloat16, return_lse: bool = False):
         """part_o [rows, D] fp32, part_lse [rows] fp32 (this rank's partial) -> merged O [rows, D] on every rank."""
         rows, d = part_o.shape
@@ -102,15 +112,23 @@ class PeerExchange:
         part_o, part_lse = part_o.contiguous(), part_lse.contiguous()
         out = torch.empty(rows, d, dtype=out_dtype, device=part_o.device)
         lse = torch.empty(rows, dtype=torch.float32, device=part_o.device) if return_lse else None
-        a = L.PeerMergeArgs()
-        for w in range(self.world):
-            a.peer_data[w], a.peer_flags[w] = self.data_ptrs[w], self.flag_ptrs[w]
-        a.rank, a.world, a.rows, a.rows_cap, a.head_dim, a.epoch = self.rank, self.world, rows, self.rows_cap, d, self.epoch.data_ptr()
-        a.part_o, a.part_lse, a.out = part_o.data_ptr(), part_lse.data_ptr(), out.data_ptr()
-        a.o_dtype = L.BF16 if out_dtype == torch.bfloat16 else L.F16
-        a.lse = None if lse is None else lse.data_ptr()
+        a = self._args(rows, out, lse)
+        a.part_o, a.part_lse = part_o.data_ptr(), part_lse.data_ptr()
         L.check(L.lib.sqattn_decode_peer_merge(C.byref(a), torch.cuda.current_stream().cuda_stream))
         return (out, lse) if return_lse else out
+
+    def decode(self, q, k_shard, v_shard, *, kv_lens=None, out_dtype=torch.bfloat16, p_fp8: bool = False):
+        """Split-KV decode of this rank's keys with the exchange fused behind it: two kernels per call (decode;
+        split merge + peer stores + wait + merge across ranks).  q [B,Hq,1,D] -> O [B,Hq,1,D] on every rank."""
+        from . import ops
+        b, hq, _, d = q.shape
+        rows = b * hq
+        if d != self.d or rows > self.rows_cap:
+            raise ValueError(f"{rows} rows x {d} do not fit an exchange of {self.rows_cap} x {self.d}")
+        out = torch.empty(rows, d, dtype=out_dtype, device=q.device)
+        a = self._args(rows, out, None)
+        ops.decode(q, k_shard, v_shard, kv_lens=kv_lens, p_fp8=p_fp8, peer=a)
+        return out.view(b, hq, 1, d)
 
 
 def shard_range(rank: int, world: int, seq_total: int):
@@ -176,13 +194,13 @@ def sp_decode(q, k_shard, v_shard, *, kv_lens: Optional[Sequence[int]] = None, o
     """Split-KV decode across ranks.  q [B,Hq,1,D] (replicated), k_shard/v_shard [B,Hkv,Ls,D]: this rank's keys
     (``kv_lens``: how many of them are valid per sequence).  Returns O [B,Hq,1,D] on every rank.  With
     ``exchange`` the partials travel by peer stores inside one merge kernel instead of an NCCL all-gather."""
+    if exchange is not None:
+        return exchange.decode(q, k_shard, v_shard, kv_lens=kv_lens, out_dtype=out_dtype, p_fp8=p_fp8)
     backend = backend or CudaBackend()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     b, hq, _, d = q.shape
     po, pl = backend.decode_partial(q, k_shard, v_shard, kv_lens, p_fp8)  # [B,Hq,D] fp32, [B,Hq] fp32
     rows = b * hq
-    if exchange is not None:
-        return exchange.merge(po.reshape(rows, d), pl.reshape(rows), out_dtype).view(b, hq, 1, d)
     if world > 1:
         packed = torch.cat([po.reshape(rows, d), pl.reshape(rows, 1)], dim=1).contiguous()   # [rows, D+1]
         gathered = torch.empty(world, rows, d + 1, dtype=torch.float32, device=packed.device)

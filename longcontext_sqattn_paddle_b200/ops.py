@@ -162,12 +162,15 @@ def k_column_sums(key: torch.Tensor) -> torch.Tensor:
 def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse: bool = False, p_fp8: bool = False,
            q_is_scaled: bool = False, kv_lens: Optional[Sequence[int]] = None, kv_len: Optional[int] = None,
            num_splits: int = 0, partial: bool = False, reference_tail: bool = False,
-           kv_lens_device: Optional[torch.Tensor] = None):
+           kv_lens_device: Optional[torch.Tensor] = None, peer=None):
     """sqattn_decode.  q [B,Hq,1,D] (HND) or [B,1,Hq,D] (NHD); k/v caches of capacity >= kv_len.
     partial=True returns (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of these keys for a later merge.
     reference_tail=True reproduces the reference kernel's zero-score padding of the last 64-key tile.
     kv_lens_device (int32 [B] on the GPU): the lengths are read by the kernel at run time and ``kv_len`` is only the
-    capacity the key ranges are planned for, so the call can sit in a CUDA graph that is replayed as the cache grows."""
+    capacity the key ranges are planned for, so the call can sit in a CUDA graph that is replayed as the cache grows.
+    peer: a filled ``_lib.PeerMergeArgs`` (dist.PeerExchange builds it): the merge of the split-KV partials, the
+    exchange with the other GPUs and the merge across GPUs happen in one kernel; returns nothing (the result is
+    written to peer.out)."""
     _require_cuda(q, k, v)
     b, hq, one, d = _shape(q, layout)
     assert one == 1
@@ -188,7 +191,10 @@ def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse:
         assert kv_lens_device.is_cuda and kv_lens_device.dtype == torch.int32 and kv_lens_device.numel() == b
         a.kv_lens_device = kv_lens_device.data_ptr()
     out = lse = po = pl = None
-    if partial:
+    if peer is not None:
+        a.peer = C.addressof(peer)
+        a.o_dtype = L.F16
+    elif partial:
         po = torch.empty(b, hq, d, dtype=torch.float32, device=q.device)
         pl = torch.empty(b, hq, dtype=torch.float32, device=q.device)
         a.partial_o, a.partial_lse = po.data_ptr(), pl.data_ptr()
@@ -207,6 +213,8 @@ def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse:
     ws = _workspace(need, q.device)
     a.workspace, a.workspace_bytes = ws.data_ptr(), need
     L.check(L.lib.sqattn_decode(C.byref(a), _stream()))
+    if peer is not None:
+        return None
     if partial:
         return po, pl
     return (out, lse) if return_lse else out

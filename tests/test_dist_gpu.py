@@ -56,6 +56,10 @@ def _worker(rank, world, port, tmp):
             a = sqdist.sp_decode(qs, kk, vv, kv_lens=mine, exchange=ex)
             n_ = sqdist.sp_decode(qs, kk, vv, kv_lens=mine)
             outs.append((a.float() - n_.float()).abs().max().item())
+        # the stand-alone exchange entry point on partials computed by a separate call
+        po, pl = ops.decode(qs, kk, vv, partial=True, kv_lens=mine)
+        m = ex.merge(po.reshape(b * hq, d), pl.reshape(b * hq)).view(b, hq, 1, d)
+        outs.append((m.float() - n_.float()).abs().max().item())
         torch.cuda.synchronize()
         ops.check_device_status()
         torch.save(torch.tensor(outs), os.path.join(tmp, f"peer_{rank}.pt"))
