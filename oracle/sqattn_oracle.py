@@ -319,7 +319,7 @@ def windowed_prefill(q_int8, k_int8, q_int4, k_int4, v, win8, win4, sink_size: i
     if mode == "relative":
         w8s = [relative_window_size(r, kv_len) for r in w8s]
         w4s = [relative_window_size(r, kv_len) for r in w4s]
-    o = torch.zeros(b, h, n, d, dtype=torch.float32)
+    o = torch.zeros(b, h, n, d, dtype=output_dtype)   # rounded block by block: the same values as rounding at the end
     lse = torch.zeros(b, h, n, dtype=torch.float32)
     nblk = (n + block_m - 1) // block_m
     blk_list = list(range(nblk)) if blocks is None else list(blocks)
@@ -347,9 +347,9 @@ def windowed_prefill(q_int8, k_int8, q_int4, k_int4, v, win8, win4, sink_size: i
                     acc, l_i, m_i = _tile_step((acc, l_i, m_i), qb, k_t, v_t, rows, start_n,
                                                block_n, stage == 4, fp8)
             valid = min(qe, n) - qs
-            o[:, hq, qs:qs + valid] = (acc / l_i[..., None])[:, :, :valid]
+            o[:, hq, qs:qs + valid] = (acc / l_i[..., None])[:, :, :valid].to(output_dtype)
             lse[:, hq, qs:qs + valid] = (torch.log2(l_i) + m_i)[:, :, :valid]
-    o = o.to(output_dtype)[..., :d_og]
+    o = o[..., :d_og]
     if tensor_layout == "NHD":
         o = o.permute(0, 2, 1, 3)
     return (o, lse) if return_lse else o
