@@ -453,6 +453,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       tc_fence_before();
       mbar_arrive(bar_p_full + 8 * (i & 1));
       if (warp == 2 && lane == 0) SQ_STAMP(i, 11);
+      if (warp == 3 && lane == 0) SQ_STAMP(i, 8);
+      if (warp == 4 && lane == 0) SQ_STAMP(i, 10);
+      if (warp == 5 && lane == 0) SQ_STAMP(i, 14);
     }
     if (ok && nsteps > 0) ok = mbar_wait(bar_o_tail, 0, cta_abort, 123);
     ok = __all_sync(0xffffffffu, ok);
