@@ -41,6 +41,30 @@ def test_decode(ops, dtype, b, hq, hkv, L, d, fp8, ref_tail):
     assert (lse.cpu() - rlse).abs().max().item() < 2e-3
 
 
+def test_decode_full_size_1m_keys(ops):
+    """One layer of the 1M-token configuration (28/4 heads, D=128, bf16, 2 x 1 GiB of keys and values): the
+    length-aware planner at its largest single-GPU size (about 150 key ranges per KV head).  The tile-by-tile
+    oracle needs a quarter of an hour for 16384 tiles, so this size is checked against the exact softmax in fp32
+    (what the tiles add up to), with the tolerance of the tiled comparison."""
+    dtype = torch.bfloat16
+    b, hq, hkv, L, d = 1, 28, 4, 1 << 20, 128
+    q, k, v = _rand((b, hq, 1, d), 7, dtype), _rand((b, hkv, L, d), 8, dtype), _rand((b, hkv, L, d), 9, dtype)
+    o, lse = ops.decode(q.cuda(), k.cuda(), v.cuda(), out_dtype=dtype, return_lse=True)
+    g = hq // hkv
+    ro = torch.empty(b, hq, 1, d)
+    rlse = torch.empty(b, hq, 1)
+    for h in range(hkv):                                  # one KV head at a time: [g, L] scores in fp32
+        s2 = (q[0, h * g:(h + 1) * g, 0].float() @ k[0, h].float().T) * (1.0 / d ** 0.5 * 1.44269504)
+        m = s2.max(dim=-1, keepdim=True).values
+        p = torch.exp2(s2 - m)
+        l = p.sum(dim=-1, keepdim=True)
+        ro[0, h * g:(h + 1) * g, 0] = (p @ v[0, h].float()) / l
+        rlse[0, h * g:(h + 1) * g] = torch.log2(l) + m
+    assert torch.isfinite(o).all()
+    assert (o.float().cpu() - ro).abs().max().item() < 2e-2
+    assert (lse.cpu() - rlse).abs().max().item() < 2e-3
+
+
 def test_decode_ragged_nhd(ops):
     dtype = torch.bfloat16
     b, hq, hkv, cap, d = 5, 32, 8, 9000, 128

@@ -169,6 +169,30 @@ def test_config2_blocks_32k(sq):
     assert torch.isfinite(out).all() and err < TOL_O, err
 
 
+def test_full_size_131072_tokens_blocks(sq):
+    """131072 tokens (the 128K configuration), 28/4 heads, D=128: the full operator on the GPU, the oracle on three
+    64-row query blocks (first, middle, last); exercises the index arithmetic at the largest single-GPU size."""
+    from longcontext_sqattn_paddle_b200.sqattn import mp_triton_wrapper
+    n, hq, hkv, d = 131072, 28, 4, 128
+    q, k, v = so.make_inputs(3, 1, n, hq, hkv, d, torch.bfloat16)
+
+    class Args:
+        qk_qtype, v_qtype, use_relative_distance = "int", "int", True
+
+    class Layer:
+        num_key_value_groups = hq // hkv
+
+    fn = mp_triton_wrapper(1, [0.1] * hq, [0.1] * hq, 256, Args())
+    out = fn(Layer(), q.cuda(), k.cuda(), v.cuda(), None).cpu()
+    blocks = [0, 1027, 2047]
+    # K/V are not repeated per query head here (groups = 1; the oracle's kernel indexes KV heads itself): the
+    # repeated copies are bit-identical and the V ranges taken over heads do not change, but 7x the memory would
+    ref = so.attention_fn(q, k, v, 1, [0.1] * hq, [0.1] * hq, 256, blocks=blocks)
+    rows = torch.cat([torch.arange(b * 64, b * 64 + 64) for b in blocks])
+    err = (out[:, rows].float() - ref[:, rows].float()).abs().max().item()
+    assert torch.isfinite(out).all() and err < TOL_O, err
+
+
 def test_errors(sq):
     q = torch.zeros(1, 2, 128, 128, dtype=torch.float16, device="cuda")
     with pytest.raises(ValueError):
