@@ -233,6 +233,25 @@ int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_ro
                        const int32_t* count, int32_t groups, int32_t cap, int32_t head_dim, void* dst,
                        sqattn_stream_t stream);
 
+/* The two calls above for every sequence of a ragged batch in two launches (select, then gather of keys and
+ * values): one item per sequence, the same geometry, budget and cap for all. */
+typedef struct sqattn_retrieve_item {
+  const void* q;                 /* [G, heads_per_group, D] */
+  const void* centroids;         /* [G, K, D] */
+  const int32_t* cluster_size;   /* [G, K] */
+  const int32_t* clusters;       /* [G, K, max_cluster_size] */
+  int32_t num_clusters, max_cluster_size, num_tokens;
+  int32_t* out_idx;              /* [G, cap] */
+  int32_t* out_count;            /* [G] */
+  const void* k_src;             /* [G, tokens, D] through the strides below (elements) */
+  const void* v_src;
+  int64_t src_group_stride, src_row_stride;
+  void* k_dst;                   /* [G, cap, D] */
+  void* v_dst;
+} sqattn_retrieve_item;
+int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, int32_t dtype, int32_t groups_kv,
+                          int32_t heads_per_group, int32_t head_dim, int32_t budget, int32_t cap, sqattn_stream_t stream);
+
 /* ---- window calibration (sqattn/window_search.py) ------------------------------------------------------ */
 
 /* Distance-weighted attention-energy histogram per query head, accumulated into hist [Hq, num_bins] (fp64, not

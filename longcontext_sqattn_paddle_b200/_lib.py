@@ -71,6 +71,13 @@ class DecodeArgs(C.Structure):
 
 
 # every symbol include/sqattn_b200.h declares: (name, restype, argtypes)
+class RetrieveItem(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("centroids", C.c_void_p), ("cluster_size", C.c_void_p), ("clusters", C.c_void_p),
+                ("num_clusters", C.c_int32), ("max_cluster_size", C.c_int32), ("num_tokens", C.c_int32),
+                ("out_idx", C.c_void_p), ("out_count", C.c_void_p), ("k_src", C.c_void_p), ("v_src", C.c_void_p),
+                ("src_group_stride", C.c_int64), ("src_row_stride", C.c_int64), ("k_dst", C.c_void_p), ("v_dst", C.c_void_p)]
+
+
 class PeerMergeArgs(C.Structure):
     _fields_ = [("peer_data", C.c_void_p * 16), ("peer_flags", C.c_void_p * 16), ("rank", C.c_int32), ("world", C.c_int32),
                 ("rows", C.c_int32), ("rows_cap", C.c_int32), ("head_dim", C.c_int32), ("epoch", C.c_void_p),
@@ -104,6 +111,8 @@ SYMBOLS = [
                                          C.c_int32, C.c_void_p]),
     ("sqattn_gather_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                      C.c_int32, C.c_void_p, C.c_void_p]),
+    ("sqattn_retrieve_batch", C.c_int, [C.POINTER(RetrieveItem), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                        C.c_int32, C.c_int32, C.c_void_p]),
     ("sqattn_window_histogram", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                           C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     ("sqattn_peer_merge_data_bytes", C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),

@@ -57,7 +57,7 @@ class RaggedClusteredDecoder:
     ``budget`` tokens per (sequence, KV head), gathers them and attends with FP8-rounded P; every
     (sequence, KV head) pair is one row of a batched split-KV decode call."""
 
-    def __init__(self, caches: Sequence[ClusteredKV], budget: int = 4096, p_fp8: bool = True):
+    def __init__(self, caches: Sequence[ClusteredKV], budget: int = 4096, p_fp8: bool = True, hq: int = 0):
         self.caches: List[ClusteredKV] = list(caches)
         self.budget, self.p_fp8 = budget, p_fp8
         c0 = self.caches[0]
@@ -68,15 +68,51 @@ class RaggedClusteredDecoder:
         self.count = torch.empty(b, self.hkv, dtype=torch.int32, device=dev)
         self.k_sel = torch.empty(b * self.hkv, 1, self.cap, self.d, dtype=dt, device=dev)
         self.v_sel = torch.empty(b * self.hkv, 1, self.cap, self.d, dtype=dt, device=dev)
+        self._q = None        # persistent copy of the step's queries: the item table below points into it
+        self._items = None
+
+    def _table(self, hq: int):
+        """One sqattn_retrieve_item per sequence; every pointer in it stays valid for the decoder's lifetime."""
+        b = len(self.caches)
+        self._q = torch.empty(b, hq, 1, self.d, dtype=self.caches[0].key.dtype, device=self.idx.device)
+        items = (L.RetrieveItem * b)()
+        for i, c in enumerate(self.caches):
+            it = items[i]
+            it.q, it.centroids = self._q[i].data_ptr(), c.centroids.data_ptr()
+            it.cluster_size, it.clusters = c.cluster_size.data_ptr(), c.clusters.data_ptr()
+            it.num_clusters, it.max_cluster_size, it.num_tokens = c.k, c.max_cluster_size, c.tokens
+            it.out_idx, it.out_count = self.idx[i].data_ptr(), self.count[i].data_ptr()
+            it.k_src, it.v_src = c.key.data_ptr(), c.value.data_ptr()
+            it.src_group_stride, it.src_row_stride = c.tokens * self.d, self.d
+            it.k_dst = self.k_sel[i * self.hkv:(i + 1) * self.hkv].data_ptr()
+            it.v_dst = self.v_sel[i * self.hkv:(i + 1) * self.hkv].data_ptr()
+        self._items = items
 
     def step(self, q: torch.Tensor, out_dtype=None) -> torch.Tensor:
+        """Four launches and no host synchronisation: select (all sequences), gather (all keys and values), split-KV
+        decode with the retrieved counts read on the device, merge."""
+        b, hq, _, d = q.shape
+        groups = hq // self.hkv
+        if self._items is None or self._q.shape[1] != hq:
+            self._table(hq)
+        self._q.copy_(q)
+        L.check(L.lib.sqattn_retrieve_batch(self._items, b, _dt(q.dtype), self.hkv, groups, d, self.budget, self.cap,
+                                            _stream()))
+        qv = self._q.view(b * self.hkv, groups, 1, d)
+        o = ops.decode(qv, self.k_sel, self.v_sel, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8, kv_len=self.cap,
+                       kv_lens_device=self.count.view(-1))
+        return o.view(b, hq, 1, d)
+
+    def step_unbatched(self, q: torch.Tensor, out_dtype=None) -> torch.Tensor:
+        """The same through the per-sequence entry points (one select and two gathers per sequence, lengths read back
+        to the host for the planner); kept as the cross-check of ``step``."""
         b, hq, _, d = q.shape
         groups = hq // self.hkv
         for i, c in enumerate(self.caches):
             c.select(q[i, :, 0], self.budget, self.cap, self.idx[i], self.count[i])
             c.gather(self.idx[i], self.count[i], self.cap, self.k_sel[i * self.hkv:(i + 1) * self.hkv, 0],
                      self.v_sel[i * self.hkv:(i + 1) * self.hkv, 0])
-        lens = self.count.flatten().tolist()   # one small device-to-host read per step (the scheduler runs on the host)
+        lens = self.count.flatten().tolist()
         qv = q.reshape(b * self.hkv, groups, 1, d)
         o = ops.decode(qv, self.k_sel, self.v_sel, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8, kv_lens=lens)
         return o.view(b, hq, 1, d)

@@ -22,7 +22,7 @@ struct RetrieveParams {
 };
 
 template <bool BF16>
-__global__ void __launch_bounds__(1024) retrieve_select_kernel(const __grid_constant__ RetrieveParams p) {
+__device__ __forceinline__ void retrieve_select_body(const RetrieveParams& p, const int g) {
   extern __shared__ __align__(16) uint8_t rs[];
   double* scores = reinterpret_cast<double*>(rs);                                   // [K]
   uint32_t* bitmap = reinterpret_cast<uint32_t*>(rs + sizeof(double) * p.num_clusters);  // [ceil(T/32)]
@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(1024) retrieve_select_kernel(const __grid_cons
   __shared__ int red_i[32];
   __shared__ int sel_list[kRetMaxClusters];
   __shared__ int n_sel, total_tok, warp_sums[32];
-  const int g = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.num_clusters, D = p.d;
   const uint16_t* q = reinterpret_cast<const uint16_t*>(p.q) + static_cast<long long>(g) * p.groups * D;
   const uint16_t* cent = reinterpret_cast<const uint16_t*>(p.cent) + static_cast<long long>(g) * K * D;
@@ -128,6 +128,44 @@ __global__ void __launch_bounds__(1024) retrieve_select_kernel(const __grid_cons
     }
   }
   if (tid == blockDim.x - 1) p.out_count[g] = min(pos, p.cap);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(1024) retrieve_select_kernel(const __grid_constant__ RetrieveParams p) {
+  retrieve_select_body<BF16>(p, blockIdx.x);
+}
+
+// All sequences of a ragged batch in one launch: blockIdx.y = sequence, blockIdx.x = KV group.
+constexpr int kRetMaxBatch = 32;
+struct RetrieveBatch {
+  RetrieveParams item[kRetMaxBatch];
+};
+template <bool BF16>
+__global__ void __launch_bounds__(1024) retrieve_select_batch_kernel(const __grid_constant__ RetrieveBatch b) {
+  retrieve_select_body<BF16>(b.item[blockIdx.y], blockIdx.x);
+}
+
+struct GatherItem {
+  const uint8_t* src;   // [G, tokens, D] through strides
+  uint8_t* dst;         // [G, cap, D]
+  const int* idx;       // [G, cap]
+  const int* count;     // [G]
+  long long src_group_stride, src_row_stride;
+};
+struct GatherBatch {
+  GatherItem item[2 * kRetMaxBatch];  // keys and values of every sequence
+};
+__global__ void gather_rows_batch_kernel(const __grid_constant__ GatherBatch b, int cap, int d) {
+  const GatherItem& it = b.item[blockIdx.z];
+  const int g = blockIdx.y, d8 = d / 8;
+  const int n = it.count[g];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < static_cast<long long>(n) * d8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i / d8), c = static_cast<int>(i % d8);
+    const int tok = it.idx[static_cast<long long>(g) * cap + j];
+    const uint4 v = *reinterpret_cast<const uint4*>(it.src + 2 * (g * it.src_group_stride + tok * it.src_row_stride + c * 8));
+    *reinterpret_cast<uint4*>(it.dst + 2 * ((static_cast<long long>(g) * cap + j) * d + c * 8)) = v;
+  }
 }
 
 // dst[g, j, :] = src[g, idx[g, j], :] for j < count[g]  (16-byte chunks; src rows `src_row_stride` elements apart)

@@ -656,6 +656,55 @@ int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_ro
   return SQATTN_OK;
 }
 
+int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, int32_t dtype, int32_t groups_kv,
+                          int32_t heads_per_group, int32_t head_dim, int32_t budget, int32_t cap, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!items || num_items <= 0) return fail(SQATTN_ERR_INVALID_ARG, "no items");
+  if (head_dim > 128 || head_dim % 8) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: at most 128, multiple of 8", head_dim);
+  if (groups_kv <= 0 || heads_per_group <= 0 || budget <= 0 || cap <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  for (int first = 0; first < num_items; first += kRetMaxBatch) {
+    const int n = num_items - first < kRetMaxBatch ? num_items - first : kRetMaxBatch;
+    RetrieveBatch rb;
+    GatherBatch gb;
+    memset(&rb, 0, sizeof(rb));
+    memset(&gb, 0, sizeof(gb));
+    size_t smem = 0;
+    for (int i = 0; i < n; ++i) {
+      const sqattn_retrieve_item& it = items[first + i];
+      if (!it.q || !it.centroids || !it.cluster_size || !it.clusters || !it.out_idx || !it.out_count || !it.k_src || !it.v_src ||
+          !it.k_dst || !it.v_dst)
+        return fail(SQATTN_ERR_INVALID_ARG, "retrieve item %d: null pointer", first + i);
+      if (it.num_clusters <= 0 || it.num_clusters > kRetMaxClusters) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d clusters supported", kRetMaxClusters);
+      if (it.num_tokens <= 0 || it.num_tokens > kRetMaxTokens) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d tokens supported", kRetMaxTokens);
+      if (it.max_cluster_size <= 0 || it.src_row_stride % 8 || it.src_group_stride % 8) return fail(SQATTN_ERR_INVALID_ARG, "retrieve item %d: bad sizes or strides", first + i);
+      RetrieveParams& p = rb.item[i];
+      p.q = static_cast<const uint8_t*>(it.q); p.cent = static_cast<const uint8_t*>(it.centroids);
+      p.cluster_size = it.cluster_size; p.clusters = it.clusters; p.out_idx = it.out_idx; p.out_count = it.out_count;
+      p.groups = heads_per_group; p.num_clusters = it.num_clusters; p.d = head_dim; p.max_cluster_size = it.max_cluster_size;
+      p.num_tokens = it.num_tokens; p.budget = budget; p.cap = cap;
+      const size_t need = sizeof(double) * it.num_clusters + sizeof(uint32_t) * ((it.num_tokens + 31) / 32);
+      smem = need > smem ? need : smem;
+      gb.item[2 * i] = GatherItem{static_cast<const uint8_t*>(it.k_src), static_cast<uint8_t*>(it.k_dst), it.out_idx, it.out_count,
+                                  it.src_group_stride, it.src_row_stride};
+      gb.item[2 * i + 1] = GatherItem{static_cast<const uint8_t*>(it.v_src), static_cast<uint8_t*>(it.v_dst), it.out_idx, it.out_count,
+                                      it.src_group_stride, it.src_row_stride};
+    }
+    const dim3 sgrid(groups_kv, n);
+    if (dtype == SQATTN_BF16) {
+      SQ_CUDA(cudaFuncSetAttribute(retrieve_select_batch_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      retrieve_select_batch_kernel<true><<<sgrid, 1024, smem, stream>>>(rb);
+    } else {
+      SQ_CUDA(cudaFuncSetAttribute(retrieve_select_batch_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      retrieve_select_batch_kernel<false><<<sgrid, 1024, smem, stream>>>(rb);
+    }
+    SQ_CUDA(cudaGetLastError());
+    const dim3 ggrid(elementwise_grid(static_cast<long long>(cap) * (head_dim / 8), 256), groups_kv, 2 * n);
+    gather_rows_batch_kernel<<<ggrid, 256, 0, stream>>>(gb, cap, head_dim);
+    SQ_CUDA(cudaGetLastError());
+  }
+  return SQATTN_OK;
+}
+
 // ---- window calibration ----------------------------------------------------------------------------------
 int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t num_q_heads, int32_t num_kv_heads,
                             int32_t seq_len, int32_t head_dim, int32_t relative, int32_t num_bins, int32_t sink,

@@ -78,6 +78,15 @@ def test_clustered_retrieval_ragged_decode():
     q = torch.randn(len(lens), hq, 1, d, generator=g).to(torch.bfloat16)
     out = dec.step(q.cuda()).cpu()
     out16 = RaggedClusteredDecoder(caches, budget=budget, p_fp8=False).step(q.cuda()).cpu()
+    # the per-sequence entry points select the same tokens; the attention then only differs in where the planner,
+    # which sees the counts on the host there, cuts the key ranges
+    idx_b, cnt_b = dec.idx.clone(), dec.count.clone()
+    out_u = dec.step_unbatched(q.cuda()).cpu()
+    assert torch.equal(cnt_b, dec.count)
+    for i in range(len(lens)):
+        for h in range(hkv):
+            assert torch.equal(idx_b[i, h, :cnt_b[i, h]], dec.idx[i, h, :cnt_b[i, h]])
+    assert (out_u.float() - out.float()).abs().max().item() < 3e-2
     groups = hq // hkv
     for i, n in enumerate(lens):
         k = ko.init_centroid_indices(n, caches[i].k).numel()
