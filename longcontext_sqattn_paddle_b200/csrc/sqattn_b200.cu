@@ -714,14 +714,31 @@ int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t
   if (head_dim % 8 || head_dim <= 0 || head_dim > 256) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d", head_dim);
   if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || seq_len <= 0 || num_bins <= 0 || sink < 0)
     return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
-  const size_t smem = (8 * static_cast<size_t>(head_dim) + num_bins) * sizeof(float);
-  if (smem > 200 * 1024) return fail(SQATTN_ERR_UNSUPPORTED, "too many bins (%d)", num_bins);
   WindowHistParams p;
   p.q = static_cast<const uint8_t*>(q); p.k = static_cast<const uint8_t*>(k); p.hist = hist;
   p.hq = num_q_heads; p.groups = num_q_heads / num_kv_heads; p.n = seq_len; p.d = head_dim; p.nbins = num_bins;
   p.sink = sink; p.relative = relative; p.scale = static_cast<float>(1.0 / sqrt(static_cast<double>(head_dim)));
+  const bool bf16 = dtype == SQATTN_BF16;
+  if (head_dim == 64 || head_dim == 128) {
+    // tensor-core kernel: Q tile + two K tiles (rows padded by 8 elements) + the block histogram
+    const size_t smem = static_cast<size_t>(3) * 64 * (head_dim + 8) * 2 + static_cast<size_t>(num_bins) * sizeof(float);
+    if (smem > 220 * 1024) return fail(SQATTN_ERR_UNSUPPORTED, "too many bins (%d)", num_bins);
+    const dim3 grid((seq_len + kWhRows - 1) / kWhRows, num_q_heads);
+#define SQ_WH(BF, DD)                                                                                                      \
+    do {                                                                                                                   \
+      SQ_CUDA(cudaFuncSetAttribute(window_hist_mma_kernel<BF, DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \
+      window_hist_mma_kernel<BF, DD><<<grid, 128, smem, stream>>>(p);                                                      \
+    } while (0)
+    if (head_dim == 128) { if (bf16) SQ_WH(true, 128); else SQ_WH(false, 128); }
+    else { if (bf16) SQ_WH(true, 64); else SQ_WH(false, 64); }
+#undef SQ_WH
+    SQ_CUDA(cudaGetLastError());
+    return SQATTN_OK;
+  }
+  const size_t smem = (8 * static_cast<size_t>(head_dim) + num_bins) * sizeof(float);
+  if (smem > 200 * 1024) return fail(SQATTN_ERR_UNSUPPORTED, "too many bins (%d)", num_bins);
   dim3 grid(elementwise_grid((seq_len + 7) / 8, 1), num_q_heads);
-  if (dtype == SQATTN_BF16) {
+  if (bf16) {
     SQ_CUDA(cudaFuncSetAttribute(window_hist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     window_hist_kernel<true><<<grid, 256, smem, stream>>>(p);
   } else {
