@@ -13,7 +13,6 @@ kernels run; the two partial results are combined by the LSE merge kernel.
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Optional
 
 import torch
