@@ -435,6 +435,12 @@ def run_kernel_only(args):
         qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16)
         fn = lambda: ops.decode(qd, kk, vv, out_dtype=torch.bfloat16)
         work, unit = 2.0 * HKV * n * D * 2 / 1e9, "GB/s"
+    elif args.kernel_only == "prep":
+        q, k, v = so.make_inputs(1000, 1, n, HQ, HKV, D, torch.bfloat16)
+        dq, dk, dv = q.to(dev), k.to(dev), v.to(dev)
+        fn = lambda: ops.prep_qkv(dq, dk, dv, skip_bit4=True)
+        # one read and one write of Q, K and V (the K mean pass reads K once more)
+        work, unit = 2.0 * 2 * n * (HQ + 2 * HKV) * D / 1e9, "GB/s"
     else:
         q, k, v = so.make_inputs(1000, 1, n, HQ, HKV, D, torch.bfloat16)
         q8, _, k8, _, v8 = ops.prep_qkv(q.to(dev), k.to(dev), v.to(dev), skip_bit4=True)
@@ -726,7 +732,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode"],
+    ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode", "prep"],
                     help="launch only this kernel --steps times on the bench tensors (for profiler captures)")
     ap.add_argument("--seq", type=int, default=None, help="sequence length for --kernel-only / --workload")
     ap.add_argument("--workload", default="operator", choices=["operator", "ttft", "decode_model", "decode_sp", "decode_hybrid", "retrieval"],
