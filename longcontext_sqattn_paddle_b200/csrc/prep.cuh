@@ -181,6 +181,52 @@ __device__ __forceinline__ void fake_quant_int8x(const float (&x)[8], float absm
   }
 }
 
+// The integer grid for the 8 values a thread holds of one row, on packed fp32 pairs, returning the 8 results
+// rounded to the 16-bit type (and, for queries, multiplied by q_scale and rounded again) as four packed words.
+// Every operation is the IEEE round-to-nearest one of the scalar path above, so the bits are the same.
+template <bool BF16, bool kScale>
+__device__ __forceinline__ uint4 fake_quant_int_row8(const float (&x)[8], float absmax, float qmax, int half_even, float q_scale) {
+  const float scale = __fdiv_rn(absmax, qmax), inv = __fdiv_rn(1.0f, scale);
+  const uint64_t inv2 = f32x2_pack(inv, inv), sc2 = f32x2_pack(scale, scale), qs2 = f32x2_pack(q_scale, q_scale);
+  float g[8];
+  float worst = 0.f;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint64_t q2 = f32x2_mul(f32x2_pack(x[2 * p], x[2 * p + 1]), inv2);
+    float q0, q1, d0, d1;
+    f32x2_unpack(q2, q0, q1);
+    const float r0 = rintf(q0), r1 = rintf(q1);
+    const uint64_t r2 = f32x2_pack(r0, r1);
+    f32x2_unpack(f32x2_sub(q2, r2), d0, d1);
+    worst = fmaxf(worst, fmaxf(fabsf(d0), fabsf(d1)));
+    f32x2_unpack(f32x2_mul(r2, sc2), g[2 * p], g[2 * p + 1]);
+  }
+  if (worst > 0.4999f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = fake_quant_value(x[i], absmax, SQATTN_QTYPE_INT, qmax, half_even);
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    uint32_t v = BF16 ? pack_bf16x2(g[2 * p], g[2 * p + 1]) : pack_f16x2(g[2 * p], g[2 * p + 1]);
+    if (kScale) {
+      float a, b;
+      if (BF16) {
+        a = __uint_as_float(v << 16);
+        b = __uint_as_float(v & 0xffff0000u);
+      } else {
+        const __half2 h2 = *reinterpret_cast<const __half2*>(&v);
+        a = __low2float(h2);
+        b = __high2float(h2);
+      }
+      f32x2_unpack(f32x2_mul(f32x2_pack(a, b), qs2), a, b);
+      v = BF16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+    }
+    w[p] = v;
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Per-token fake-quant of Q or K.  Input [B,N,H,D] via strides, outputs contiguous [B,H,N,D].
 // kIsK: subtract the (dtype-rounded) sequence mean first, no scaling of the result.
 // Q: results are multiplied by 1/sqrt(D)*log2e in the input dtype.
@@ -228,30 +274,19 @@ quant_rows_kernel(View4 x, const float* mean, uint8_t* out8, uint8_t* out4, OutS
       for (int o = d8 / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp_mask, amax, o));
       amax = fmaxf(amax, 1e-5f);
       if (live[u]) {
-        float g[8];
-        if (qtype == SQATTN_QTYPE_INT) {
-          fake_quant_int8x(f, amax, 127.0f, half_even, g);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) g[i] = to_f32<BF16>(from_f32<BF16>(g[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
-        }
-        if (!kIsK) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) g[i] *= q_scale;
-        }
         const long long ooff = out_base + static_cast<long long>(n0 + u * rows_per_block) * os.sn * 2;
-        *reinterpret_cast<uint4*>(out8 + ooff) = pack8<BF16>(g);
-        if (out4) {
-          fake_quant_int8x(f, amax, 7.0f, half_even, g);
+        if (qtype == SQATTN_QTYPE_INT) {
+          *reinterpret_cast<uint4*>(out8 + ooff) = fake_quant_int_row8<BF16, !kIsK>(f, amax, 127.0f, half_even, q_scale);
+        } else {
+          float g[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            g[i] = to_f32<BF16>(from_f32<BF16>(g[i]));
+            g[i] = to_f32<BF16>(from_f32<BF16>(fake_quant_value(f[i], amax, qtype, 127.0f, half_even)));
             if (!kIsK) g[i] *= q_scale;
           }
-          *reinterpret_cast<uint4*>(out4 + ooff) = pack8<BF16>(g);
+          *reinterpret_cast<uint4*>(out8 + ooff) = pack8<BF16>(g);
         }
+        if (out4) *reinterpret_cast<uint4*>(out4 + ooff) = fake_quant_int_row8<BF16, !kIsK>(f, amax, 7.0f, half_even, q_scale);
       }
     }
   }
