@@ -80,6 +80,14 @@ typedef struct {
   size_t workspace_bytes;
   int32_t q_row_offset; /* sequence-parallel shards: q/o hold rows [q_row_offset, q_row_offset + qo_len) of a
                            kv_len-token sequence (multiple of 128); 0 for a whole sequence */
+  int32_t q_split_rows; /* 0: one row range.  Otherwise q/o rows [q_split_rows, qo_len) are sequence rows starting at
+                           q_row_offset2 (both multiples of 128): a rank that owns two separate row ranges, e.g. chunks
+                           r and 2G-1-r of the zig-zag split that balances causal work, runs them in one launch */
+  int32_t q_row_offset2;
+  int32_t head_dim_og;  /* 0 or head_dim: nothing special.  Otherwise the tensors were zero-padded from head_dim_og
+                           to head_dim (64 or 128) by the caller and the softmax scale applied when q_is_scaled == 0
+                           is 1/sqrt(head_dim_og), as the reference launchers do (sqattn/attn_triton.py:236-253, 314;
+                           attn_triton_mix_relative.py:369-385); the caller slices the output back */
 } sqattn_prefill_args;
 
 /* Replaces the launch halves of attn_causal / attn_hierarchical_relative_window /
@@ -161,6 +169,8 @@ typedef struct {
    * them with the other ranks and merges across ranks (see sqattn_decode_peer_merge; its part_o / part_lse are
    * ignored, its out / lse receive the result; o, lse, partial_o and partial_lse of this struct are not used). */
   const struct sqattn_peer_merge_args* peer;
+  int32_t head_dim_og;     /* as in sqattn_prefill_args: the un-padded head_dim the softmax scale is taken from when
+                              q_is_scaled == 0 (attn_triton_decode.py:254-271); 0 = head_dim */
 } sqattn_decode_args;
 
 /* Replaces attn_unified's decode branch + _attn_decode_fwd, sqattn/attn_triton_decode.py:175-241,
@@ -320,12 +330,28 @@ int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32
 int sqattn_cache_copy_rows(void* dst, int64_t dst_row_stride_bytes, const void* src, int64_t src_row_stride_bytes,
                            int64_t row_bytes, int64_t rows, int32_t to_device, sqattn_stream_t stream);
 
+/* The decode-time append of flash_attn_cache.decode_update_kv_cache (cache_hub/flash_attn_cache.py:239-256):
+ * k_cache[b, positions[b], :] = k_new[b, :] and the same for v, for every sequence b, in one launch.  Caches are
+ * [batch, capacity, row_elems] 16-bit through the two strides (elements), k_new / v_new [batch, row_elems] with
+ * new_seq_stride between sequences, positions a DEVICE int64 [batch] (so a captured graph can be replayed while
+ * they advance); positions outside [0, capacity) are skipped.  row_elems = Hkv * head_dim, a multiple of 8. */
+int sqattn_cache_append(void* k_cache, void* v_cache, const void* k_new, const void* v_new, const int64_t* positions,
+                        int64_t cache_seq_stride, int64_t cache_row_stride, int64_t new_seq_stride, int32_t batch,
+                        int32_t row_elems, int64_t capacity, sqattn_stream_t stream);
+
 /* ---- diagnostics -------------------------------------------------------------------------- */
 
-/* Device-side waits (TMA / tensor-core completion barriers) are bounded; a wait that gives up records a
- * code in a device word that this call reads back (it synchronises the stream).  Returns SQATTN_OK or
- * SQATTN_ERR_DEVICE_TIMEOUT. */
+/* Device-side waits (TMA / tensor-core completion barriers, the peer wait of the cross-GPU merge) are bounded; a
+ * wait that gives up records a code in a device word that this call reads back and clears (it synchronises the
+ * stream).  Returns SQATTN_OK or SQATTN_ERR_DEVICE_TIMEOUT.  While the word is set, every later attention or
+ * decode launch on that device fills its output with NaN instead of computing (the failure cannot pass for a
+ * result), until this call has cleared it. */
 int sqattn_check_device_status(sqattn_stream_t stream);
+/* Optional mirror of that word in host memory, so that a caller can notice a failure without synchronising:
+ * host_word is a caller-owned int32 in pinned, device-mapped host memory (or NULL to switch the mirror off) that
+ * must stay valid while kernels of this library may run on the current device; a wait that gives up also stores
+ * its code there.  The caller reads (and clears) the word itself; sqattn_check_device_status does not touch it. */
+int sqattn_set_status_mirror(int32_t* host_word);
 const char* sqattn_last_error_string(void);
 int sqattn_version(void);
 

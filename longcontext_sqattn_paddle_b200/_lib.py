@@ -41,7 +41,8 @@ class PrefillArgs(C.Structure):
         ("win8_sizes", C.POINTER(C.c_int32)), ("win4_sizes", C.POINTER(C.c_int32)),
         ("p_fp8_mode", C.c_int32), ("q_is_scaled", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("q_row_offset", C.c_int32),
+        ("q_row_offset", C.c_int32), ("q_split_rows", C.c_int32), ("q_row_offset2", C.c_int32),
+        ("head_dim_og", C.c_int32),
     ]
 
 
@@ -67,6 +68,7 @@ class DecodeArgs(C.Structure):
         ("num_splits", C.c_int32), ("reference_tail", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("kv_lens_device", C.c_void_p), ("peer", C.c_void_p),
+        ("head_dim_og", C.c_int32),
     ]
 
 
@@ -127,7 +129,10 @@ SYMBOLS = [
     ("sqattn_silu_mul", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]),
     ("sqattn_cache_copy_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
                                          C.c_void_p]),
+    ("sqattn_cache_append", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                      C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
     ("sqattn_check_device_status", C.c_int, [C.c_void_p]),
+    ("sqattn_set_status_mirror", C.c_int, [C.c_void_p]),
     ("sqattn_last_error_string", C.c_char_p, []),
     ("sqattn_version", C.c_int, []),
 ]

@@ -85,14 +85,16 @@ class flash_attn_cache:
         if layer_idx == 0 and self.valid_length_host[start_bdx] != valid:
             self.valid_length[start_bdx] = valid
             self.valid_length_host[start_bdx] = valid
+        # a dtype conversion runs on the producing stream: it has to be enqueued BEFORE the event the copy stream waits on
+        srcs = []
+        for states in (key_states, value_states):
+            src = states[0, vs:vs + valid]                               # may be a strided view of a fused projection
+            srcs.append(src if src.dtype == self.dtype else src.to(self.dtype))
         ready = torch.cuda.Event()
         ready.record()
         self.copystream.wait_event(ready)
-        for cache, states in ((self.key_cache, key_states), (self.value_cache, value_states)):
+        for cache, src in ((self.key_cache, srcs[0]), (self.value_cache, srcs[1])):
             dst = cache[layer_idx][start_bdx, :valid]                    # [valid, Hkv, D], contiguous
-            src = states[0, vs:vs + valid]                               # may be a strided view of a fused projection
-            if src.dtype != self.dtype:
-                src = src.to(self.dtype)
             src.record_stream(self.copystream)
             if self.allocated:
                 with torch.cuda.stream(self.copystream):
@@ -120,8 +122,17 @@ class flash_attn_cache:
     def decode_update_kv_cache(self, key_states, value_states, layer_idx):
         """Append one token per sequence at ``valid_length`` and return the whole layer cache
         (flash_attn_cache.py:239-256)."""
-        self.key_cache[layer_idx][self.batch_indices, self.valid_length] = key_states[:, 0]
-        self.value_cache[layer_idx][self.batch_indices, self.valid_length] = value_states[:, 0]
+        kc, vc = self.key_cache[layer_idx], self.value_cache[layer_idx]
+        kn, vn = key_states[:, 0], value_states[:, 0]                    # [B, Hkv, D], possibly views of a fused projection
+        if kn.dtype != self.dtype or not kn[0].is_contiguous() or kn.data_ptr() % 16:
+            kn = kn.to(self.dtype).contiguous()
+        if vn.dtype != self.dtype or not vn[0].is_contiguous() or vn.data_ptr() % 16:
+            vn = vn.to(self.dtype).contiguous()
+        row = kc.shape[2] * kc.shape[3]
+        L.check(L.lib.sqattn_cache_append(kc.data_ptr(), vc.data_ptr(), kn.data_ptr(), vn.data_ptr(),
+                                          self.valid_length.data_ptr(), kc.stride(0), kc.stride(1),
+                                          kn.stride(0) if kn.shape[0] > 1 else row, self.batch_size, row, kc.shape[1],
+                                          torch.cuda.current_stream().cuda_stream))
         if layer_idx == self.layer_num - 1:
             self.context += 1
             self.valid_length += 1

@@ -85,7 +85,20 @@ __global__ void __launch_bounds__(160, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ DecodeParams p) {
   using L = DecodeSmem<D>;
-  if (*reinterpret_cast<volatile int*>(&g_device_status) != 0) return;
+  // after a wait has given up on this device (here or in an earlier launch) the partials of this work item are
+  // marked invalid, so that the merge hands NaN to the caller instead of stale scratch
+  auto poison_partials = [&](int nthr) {
+    const float nan = __int_as_float(0x7fc00000);
+    for (int idx = threadIdx.x; idx < p.groups * D; idx += nthr) {
+      const long long orow = static_cast<long long>(blockIdx.x) * p.hq + blockIdx.y * p.groups + idx / D;
+      p.part_o[orow * D + idx % D] = nan;
+      if (idx % D == 0) p.part_lse[orow] = nan;
+    }
+  };
+  if (device_failed()) {
+    poison_partials(blockDim.x);
+    return;
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -275,7 +288,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       my[16 * D + 16 + g] = l_r[0]; my[16 * D + 16 + g + 8] = l_r[1];
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (ok) {
+    // the abort flag is stable here: the producer has issued its last copy before the consumers pass the last
+    // full barrier, and a consumer that gave up did so before the barrier above
+    if (*cta_abort) {
+      poison_partials(128);
+    } else if (ok) {
       for (int idx = threadIdx.x; idx < p.groups * D; idx += 128) {
         const int row = idx / D, col = idx % D;
         float mw[4], mmax = -INFINITY;
@@ -377,12 +394,12 @@ __global__ void __launch_bounds__(128 * kMergeGroups) decode_merge_kernel(const 
 #pragma unroll
     for (int g = 0; g < kMergeGroups; ++g) acc += (g < nthr / 128) ? red_s[g][tid] : 0.f;
     const int col = tid;
-    const float val = (den > 0.f) ? acc / den : 0.f;
+    const float val = (den > 0.f) ? acc / den : (den == den ? 0.f : den);  // a NaN partial (failed launch) stays NaN
     const long long off = p.contiguous ? row * p.d + col : b * p.o_sb + h * p.o_sh + col;
     if (p.o_f32) reinterpret_cast<float*>(p.o)[off] = val;
     else if (p.o_dtype) reinterpret_cast<uint16_t*>(p.o)[off] = from_f32<true>(val);
     else reinterpret_cast<uint16_t*>(p.o)[off] = from_f32<false>(val);
-    if (col == 0 && p.lse) p.lse[row] = (den > 0.f) ? log2f(den) + mmax : -INFINITY;
+    if (col == 0 && p.lse) p.lse[row] = (den > 0.f) ? log2f(den) + mmax : (den == den ? -INFINITY : den);
   }
 }
 

@@ -115,4 +115,25 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint8_t* __restrict
   }
 }
 
+// Append one new token per sequence to a layer's K and V caches: cache[b, pos[b], :] = fresh[b, :] for both tensors in
+// one launch (cache_hub/flash_attn_cache.py:239-256 does it with two indexed assignments).  pos lives on the
+// device (int64), so the call can sit in a captured graph while the positions advance; a position outside
+// [0, capacity) is skipped.  Rows are row_elems 16-bit values, moved as 16-byte pieces.
+__global__ void __launch_bounds__(256) cache_append_kernel(uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache,
+                                                           const uint8_t* __restrict__ k_new, const uint8_t* __restrict__ v_new,
+                                                           const long long* __restrict__ pos, long long cache_seq_stride,
+                                                           long long cache_row_stride, long long new_seq_stride, int batch,
+                                                           int row_elems, long long capacity) {
+  const int vec = row_elems / 8;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < 2 * batch * vec; idx += gridDim.x * blockDim.x) {
+    const int which = idx / (batch * vec), rem = idx % (batch * vec);
+    const int b = rem / vec, c = rem % vec;
+    const long long at = pos[b];
+    if (at < 0 || at >= capacity) continue;
+    const uint8_t* src = (which ? v_new : k_new) + 2 * (b * new_seq_stride) + 16 * c;
+    uint8_t* dst = (which ? v_cache : k_cache) + 2 * (b * cache_seq_stride + at * cache_row_stride) + 16 * c;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+  }
+}
+
 }  // namespace sq

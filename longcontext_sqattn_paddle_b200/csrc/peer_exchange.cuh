@@ -54,7 +54,9 @@ __global__ void __launch_bounds__(128 * kMergeGroups) peer_merge_kernel(const __
   const int tid = threadIdx.x, nthr = blockDim.x, row = blockIdx.x;
   const int dp = p.d + 1;
   const size_t parity_off = static_cast<size_t>(epoch & 1u) * p.world * p.rows_cap * dp;
-  if (tid == 0) abort_s = 0;
+  if (tid == 0) abort_s = device_failed() ? 1 : 0;   // an earlier failure on this device: no exchange, NaN out
+  __syncthreads();
+  const bool skip = abort_s != 0;
 
   // 0. this rank's partial of the row: given, or merged here from the split-KV partials of the decode kernel
   //    (same arithmetic and summation order as decode_merge_kernel)
@@ -95,13 +97,13 @@ __global__ void __launch_bounds__(128 * kMergeGroups) peer_merge_kernel(const __
       float acc = 0.f;
 #pragma unroll
       for (int g = 0; g < kMergeGroups; ++g) acc += (count > 0 && g < nthr / 128) ? red_s[g][tid] : 0.f;
-      my_val = (den > 0.f) ? acc / den : 0.f;
+      my_val = (den > 0.f) ? acc / den : (den == den ? 0.f : den);
     }
-    my_lse = (den > 0.f) ? log2f(den) + mmax : -INFINITY;
+    my_lse = (den > 0.f) ? log2f(den) + mmax : (den == den ? -INFINITY : den);
   }
 
   // 1. the row into slot `rank` of every rank's buffer
-  for (int w = 0; w < p.world; ++w) {
+  for (int w = 0; w < p.world && !skip; ++w) {
     float* dst = p.data[w] + parity_off + (static_cast<size_t>(p.rank) * p.rows_cap + row) * dp;
     if (tid < p.d) dst[tid] = my_val;
     if (tid == 0) dst[p.d] = my_lse;
@@ -109,7 +111,7 @@ __global__ void __launch_bounds__(128 * kMergeGroups) peer_merge_kernel(const __
   __threadfence_system();
   __syncthreads();
   // 2. publish, 3. wait for the same row of every rank (bounded: one second, then the status word is set)
-  if (tid < p.world) {
+  if (tid < p.world && !skip) {
     st_release_sys(p.flags[tid] + static_cast<size_t>(p.rank) * p.rows_cap + row, epoch);
     const uint32_t* mine = p.flags[p.rank] + static_cast<size_t>(tid) * p.rows_cap + row;
     const uint64_t t0 = globaltimer_ns();
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(128 * kMergeGroups) peer_merge_kernel(const __
     }
     if (!ok) {
       abort_s = 1;
-      atomicCAS(&g_device_status, 0, 301);
+      record_failure(301);
     }
   }
   __syncthreads();
@@ -139,12 +141,16 @@ __global__ void __launch_bounds__(128 * kMergeGroups) peer_merge_kernel(const __
       if (tid < p.d) acc += wt * __ldcv(rw + tid);
     }
     if (tid < p.d) {
-      const float val = (den > 0.f) ? acc / den : 0.f;
+      const float val = (den > 0.f) ? acc / den : (den == den ? 0.f : den);
       const size_t off = static_cast<size_t>(row) * p.d + tid;
       if (p.o_dtype) reinterpret_cast<uint16_t*>(p.out)[off] = from_f32<true>(val);
       else reinterpret_cast<uint16_t*>(p.out)[off] = from_f32<false>(val);
     }
     if (tid == 0 && p.lse) p.lse[row] = (den > 0.f) ? log2f(den) + mmax : -INFINITY;
+  } else {
+    // the wait gave up (or an earlier one on this device did): the row is marked invalid
+    if (tid < p.d) reinterpret_cast<uint16_t*>(p.out)[static_cast<size_t>(row) * p.d + tid] = p.o_dtype ? 0x7fc0 : 0x7e00;
+    if (tid == 0 && p.lse) p.lse[row] = __int_as_float(0x7fc00000);
   }
   // 5. the last CTA of the launch advances the step counter (every CTA has read it by now)
   __syncthreads();

@@ -40,8 +40,11 @@ struct PrefillParams {
   long long* dump_t;  // debug builds only: clock64 stamps of CTA 0, [step][16]
   int batch, hq, hkv, groups, n, kv_len;
   int mode, sink, p_fp8_mode, o_dtype, qk_bf16, same_opset, nblk;
-  int blk0;     // first 128-row block of this launch inside the whole sequence (sequence-parallel shards)
-  int n_total;  // blk0 * 128 + n: rows of the whole sequence up to the end of this shard
+  // Sequence-parallel shards: the launch's local 128-row blocks [0, blk_split) are blocks blk0.. of the whole
+  // sequence and the blocks from blk_split on are blocks blk0_b.. (a rank may own two separate row ranges, e.g. the
+  // zig-zag split that balances causal work); blk_split == nblk for a single range.
+  int blk0, blk_split, blk0_b;
+  int n_total;  // rows of the whole sequence (a 64-row half that starts at or after it does not exist)
   int w8[kMaxHeads];
   int w4[kMaxHeads];
 };
@@ -161,6 +164,24 @@ struct StepIter {
   }
 };
 
+// A CTA that cannot deliver its rows (a wait gave up here or earlier on this device) fills them with NaN so
+// that the failure cannot pass for a result.
+template <int D>
+__device__ __forceinline__ void poison_output(const PrefillParams& p, int bi, int head, int blk) {
+  const uint32_t nan2 = p.o_dtype ? 0x7fc07fc0u : 0x7e007e00u;
+  const uint4 v = make_uint4(nan2, nan2, nan2, nan2);
+  for (int idx = threadIdx.x; idx < kBlockM * (D / 8); idx += blockDim.x) {
+    const int row_local = blk * kBlockM + idx / (D / 8);
+    if (row_local >= p.n) break;
+    uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                    2 * (static_cast<long long>(bi) * p.o_sb + static_cast<long long>(head) * p.o_sh +
+                         static_cast<long long>(row_local) * p.o_sn);
+    reinterpret_cast<uint4*>(orow)[idx % (D / 8)] = v;
+    if (p.lse && idx % (D / 8) == 0)
+      p.lse[(static_cast<long long>(bi) * p.hq + head) * p.n + row_local] = __int_as_float(0x7fc00000);
+  }
+}
+
 template <int D, bool kDump, int KS_, int VS_, int kMinCtas>
 __global__ void __launch_bounds__(192, kMinCtas)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
@@ -175,13 +196,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     if (kDump && blockIdx.x == 0 && p.dump_t) p.dump_t[(step) * 16 + (slot)] = clock64(); \
   } while (0)
 
-  // once a wait has given up anywhere, the remaining CTAs of the grid leave at once
-  if (*reinterpret_cast<volatile int*>(&g_device_status) != 0) return;
+  // Heads vary fastest so that the heads of one KV group run together and share K/V tiles in L2;
+  // later (for dense causal: longer) query blocks are launched first.
+  const int per_blk = p.hq * p.batch;
+  const int blk = p.nblk - 1 - static_cast<int>(blockIdx.x) / per_blk;
+  const int rem = static_cast<int>(blockIdx.x) % per_blk;
+  const int bi = rem / p.hq, head = rem % p.hq, kvh = head / p.groups;
+  const int gblk = blk < p.blk_split ? p.blk0 + blk : p.blk0_b + (blk - p.blk_split);  // block of the whole sequence
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
-  if (sbase & 1023u) {  // the 128-byte swizzle needs 1024-byte aligned tiles: refuse to run rather than compute garbage
-    if (threadIdx.x == 0) atomicCAS(&g_device_status, 0, 100);
+  // the 128-byte swizzle needs 1024-byte aligned tiles: refuse to run rather than compute garbage
+  if ((sbase & 1023u) && threadIdx.x == 0) record_failure(100);
+  // once a wait has given up anywhere on this device, the remaining CTAs (and every later launch, until the host
+  // has read and cleared the status word) only mark their rows as invalid
+  if ((sbase & 1023u) || device_failed()) {
+    poison_output<D>(p, bi, head, blk);
     return;
   }
   const uint32_t q_s = sbase + L::kQOff, k_s = sbase + L::kKOff, v_s = sbase + L::kVOff;
@@ -196,16 +226,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
   Seg* segs = reinterpret_cast<Seg*>(smem + L::kSegOff);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Heads vary fastest so that the heads of one KV group run together and share K/V tiles in L2;
-  // later (for dense causal: longer) query blocks are launched first.
-  const int per_blk = p.hq * p.batch;
-  const int blk = p.nblk - 1 - static_cast<int>(blockIdx.x) / per_blk;
-  const int rem = static_cast<int>(blockIdx.x) % per_blk;
-  const int bi = rem / p.hq, head = rem % p.hq, kvh = head / p.groups;
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
-    *nseg_s = build_schedule(segs, p, blk + p.blk0, head);
+    *nseg_s = build_schedule(segs, p, gblk, head);
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
     for (int i = 0; i < KS; ++i) mbar_init(bar_k_full + 8 * i, 1);
@@ -344,7 +368,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     const int row_in_tile = quarter * 32 + lane;
     const int half_bit = (row_in_tile >= 64) ? kSegAct1 : kSegAct0;
     const int row_local = blk * kBlockM + row_in_tile;
-    const int row = row_local + p.blk0 * kBlockM;  // position in the whole sequence (causal mask)
+    const int row = gblk * kBlockM + row_in_tile;  // position in the whole sequence (causal mask)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_i = -INFINITY, base = -INFINITY, l_i = 1.0f;  // running maximum; reference of P, l_i and O
     bool ok = true;
@@ -495,6 +519,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   __syncthreads();
+  if (*cta_abort) poison_output<D>(p, bi, head, blk);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);

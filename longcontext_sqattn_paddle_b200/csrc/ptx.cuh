@@ -46,6 +46,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Device status word: 0 = fine, otherwise the code of the first wait that gave up.
 __device__ int g_device_status = 0;
+// Optional mirror of the status word in device-mapped host memory (sqattn_set_status_mirror): a caller can then
+// notice a failure by reading its own word, without synchronising the stream.
+__device__ int* g_status_mirror = nullptr;
+
+__device__ __forceinline__ void record_failure(int code) {
+  if (atomicCAS(&g_device_status, 0, code) == 0) {
+    int* mirror = *reinterpret_cast<int* volatile*>(&g_status_mirror);
+    if (mirror) {
+      *reinterpret_cast<volatile int*>(mirror) = code;
+      __threadfence_system();
+    }
+  }
+}
+__device__ __forceinline__ bool device_failed() { return *reinterpret_cast<volatile int*>(&g_device_status) != 0; }
 
 constexpr uint64_t kWaitLimitNs = 1000000000ull;  // every device-side wait gives up after one second
 
@@ -64,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
   *cta_abort = 1;
-  atomicCAS(&g_device_status, 0, code);
+  record_failure(code);
   return false;
 }
 

@@ -18,7 +18,11 @@ using namespace sq;
 
 namespace {
 
-double sm_scale_log2(int head_dim) { return 1.0 / sqrt(static_cast<double>(head_dim)) * 1.44269504; }
+// softmax scale in the base-2 domain; head_dim_og > 0: the tensors were zero-padded from that head_dim and the
+// scale follows the original one (sqattn/attn_triton.py:249-253)
+double sm_scale_log2(int head_dim, int head_dim_og = 0) {
+  return 1.0 / sqrt(static_cast<double>(head_dim_og > 0 ? head_dim_og : head_dim)) * 1.44269504;
+}
 
 int elementwise_grid(long long work_items, int block) {
   long long g = (work_items + block - 1) / block;
@@ -62,11 +66,25 @@ int plan_prefill(const sqattn_prefill_args* a, PrefillPlan* pl) {
     return fail(SQATTN_ERR_INVALID_ARG, "batch/heads/lengths must be positive");
   if (a->num_q_heads % a->num_kv_heads) return fail(SQATTN_ERR_INVALID_ARG, "num_q_heads must be a multiple of num_kv_heads");
   if (a->num_q_heads > kMaxHeads) return fail(SQATTN_ERR_UNSUPPORTED, "more than %d query heads", kMaxHeads);
+  if (a->head_dim_og < 0 || a->head_dim_og > a->head_dim)
+    return fail(SQATTN_ERR_INVALID_ARG, "head_dim_og %d must lie in [0, head_dim %d]", a->head_dim_og, a->head_dim);
   if (a->q_row_offset < 0 || a->q_row_offset % 128)
     return fail(SQATTN_ERR_INVALID_ARG, "q_row_offset must be a non-negative multiple of 128, got %d", a->q_row_offset);
-  if (a->q_row_offset + a->qo_len != a->kv_len && !(a->q_row_offset + a->qo_len < a->kv_len && a->qo_len % 128 == 0))
-    return fail(SQATTN_ERR_INVALID_ARG, "qo_len and kv_len must be equal for causal attention "
-                "(a shard of query rows needs q_row_offset + qo_len <= kv_len and qo_len %% 128 == 0)");
+  if (a->q_split_rows < 0 || a->q_split_rows % 128 || a->q_split_rows > a->qo_len || a->q_row_offset2 < 0 || a->q_row_offset2 % 128)
+    return fail(SQATTN_ERR_INVALID_ARG, "q_split_rows (%d) and q_row_offset2 (%d) must be non-negative multiples of 128, "
+                "q_split_rows at most qo_len", a->q_split_rows, a->q_row_offset2);
+  {
+    // every row range of the shard must end inside the sequence, and on a 128-row boundary unless it ends the sequence
+    const int len_a = a->q_split_rows > 0 ? a->q_split_rows : a->qo_len;
+    const int end_a = a->q_row_offset + len_a;
+    const int end_b = a->q_split_rows > 0 ? a->q_row_offset2 + (a->qo_len - a->q_split_rows) : end_a;
+    const bool ok_a = end_a == a->kv_len || (end_a < a->kv_len && len_a % 128 == 0);
+    const bool ok_b = end_b == a->kv_len || (end_b < a->kv_len && (a->qo_len - a->q_split_rows) % 128 == 0);
+    if (!ok_a || !ok_b)
+      return fail(SQATTN_ERR_INVALID_ARG, "qo_len and kv_len must be equal for causal attention "
+                  "(a shard of query rows needs every row range to end at or before kv_len, on a multiple of 128 rows "
+                  "unless it ends the sequence)");
+  }
   const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
   const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
   const size_t qbytes = static_cast<size_t>(a->batch) * a->num_q_heads * a->qo_len * a->head_dim * 2;
@@ -89,7 +107,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
   const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-  const float scale = static_cast<float>(sm_scale_log2(D));
+  const float scale = static_cast<float>(sm_scale_log2(D, a->head_dim_og));
   const bool bf16 = a->qk_dtype == SQATTN_BF16;
 
   sqattn_tensor q8 = a->q_int8, q4 = alias ? a->q_int8 : a->q_int4, v = a->v;
@@ -134,7 +152,9 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   p.batch = B; p.hq = Hq; p.hkv = Hkv; p.groups = Hq / Hkv; p.n = N; p.kv_len = a->kv_len;
   p.mode = a->mode; p.sink = a->sink_size; p.p_fp8_mode = a->p_fp8_mode; p.o_dtype = a->o_dtype;
   p.qk_bf16 = bf16; p.same_opset = alias; p.nblk = (N + kBlockM - 1) / kBlockM;
-  p.blk0 = a->q_row_offset / kBlockM; p.n_total = a->q_row_offset + N;
+  p.blk0 = a->q_row_offset / kBlockM; p.n_total = a->kv_len;
+  p.blk_split = a->q_split_rows > 0 ? a->q_split_rows / kBlockM : p.nblk;
+  p.blk0_b = a->q_row_offset2 / kBlockM;
   for (int h = 0; h < Hq; ++h) {
     if (a->mode == SQATTN_MODE_RELATIVE_WINDOW) {
       p.w8[h] = relative_window(a->win8_ratios[h], a->kv_len);
@@ -205,11 +225,15 @@ int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
   if (a->batch <= 0 || a->batch > kDecMaxBatch) return fail(SQATTN_ERR_UNSUPPORTED, "batch must be in [1, %d]", kDecMaxBatch);
   if (a->num_kv_heads <= 0 || a->num_q_heads % a->num_kv_heads) return fail(SQATTN_ERR_INVALID_ARG, "bad head counts");
   if (a->num_q_heads / a->num_kv_heads > 16) return fail(SQATTN_ERR_UNSUPPORTED, "more than 16 query heads per KV head");
+  if (a->head_dim_og < 0 || a->head_dim_og > a->head_dim)
+    return fail(SQATTN_ERR_INVALID_ARG, "head_dim_og %d must lie in [0, head_dim %d]", a->head_dim_og, a->head_dim);
   if (a->kv_lens_device && a->kv_lens) return fail(SQATTN_ERR_INVALID_ARG, "kv_lens and kv_lens_device are exclusive: device lengths are planned for kv_len");
   long long total_tiles = 0;
   for (int b = 0; b < a->batch; ++b) {
     const int len = a->kv_lens ? a->kv_lens[b] : a->kv_len;
     if (len < 0) return fail(SQATTN_ERR_INVALID_ARG, "kv length of sequence %d is %d", b, len);
+    if (a->kv_lens && a->kv_len > 0 && len > a->kv_len)
+      return fail(SQATTN_ERR_INVALID_ARG, "kv length of sequence %d is %d but the cache holds %d keys", b, len, a->kv_len);
     pl->lens[b] = len;
     total_tiles += (len + kDecTile - 1) / kDecTile;
   }
@@ -281,15 +305,19 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   p.part_lse = reinterpret_cast<float*>(ws + align_up(rows * D * 4, 256));
   p.batch = a->batch; p.hq = a->num_q_heads; p.hkv = a->num_kv_heads; p.groups = a->num_q_heads / a->num_kv_heads; p.d = D;
   p.chunk = pl.chunk; p.p_fp8 = a->p_fp8; p.q_is_scaled = a->q_is_scaled; p.reference_tail = a->reference_tail;
-  p.sm_scale = static_cast<float>(sm_scale_log2(D));
+  p.sm_scale = static_cast<float>(sm_scale_log2(D, a->head_dim_og));
   memcpy(p.lens, pl.lens, sizeof(int) * a->batch);
   p.lens_dev = a->kv_lens_device;
   memcpy(p.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
   using L = DecodeSmem<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    SQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
-    attr_set = true;
+  // a function attribute belongs to the current device: set on every call, like the prefill launch does
+  SQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
+  PeerMergeParams pm;
+  if (a->peer) {  // checked before anything is launched
+    if ((rc = fill_peer_params(a->peer, &pm))) return rc;
+    if (a->peer->rows != a->batch * a->num_q_heads || a->peer->head_dim != D)
+      return fail(SQATTN_ERR_INVALID_ARG, "peer merge: %d rows x %d expected, exchange describes %d x %d",
+                  a->batch * a->num_q_heads, D, a->peer->rows, a->peer->head_dim);
   }
   if (pl.total_items > 0) {
     dim3 grid(pl.total_items, a->num_kv_heads);
@@ -299,11 +327,6 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
 
   if (a->peer) {
     // the split-KV merge, the exchange with the other GPUs and the merge across GPUs in one kernel
-    PeerMergeParams pm;
-    if ((rc = fill_peer_params(a->peer, &pm))) return rc;
-    if (a->peer->rows != a->batch * a->num_q_heads || a->peer->head_dim != D)
-      return fail(SQATTN_ERR_INVALID_ARG, "peer merge: %d rows x %d expected, exchange describes %d x %d",
-                  a->batch * a->num_q_heads, D, a->peer->rows, a->peer->head_dim);
     pm.part_o = p.part_o; pm.part_lse = p.part_lse; pm.split_mode = 1; pm.hq = a->num_q_heads;
     memcpy(pm.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
     peer_merge_kernel<<<static_cast<unsigned>(pm.rows), 128 * kMergeGroups, 0, stream>>>(pm);
@@ -840,6 +863,27 @@ int sqattn_cache_copy_rows(void* dst, int64_t dst_row_stride_bytes, const void* 
   return SQATTN_OK;
 }
 
+int sqattn_cache_append(void* k_cache, void* v_cache, const void* k_new, const void* v_new, const int64_t* positions,
+                        int64_t cache_seq_stride, int64_t cache_row_stride, int64_t new_seq_stride, int32_t batch,
+                        int32_t row_elems, int64_t capacity, sqattn_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!k_cache || !v_cache || !k_new || !v_new || !positions) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (batch <= 0 || row_elems <= 0 || row_elems % 8 || capacity <= 0)
+    return fail(SQATTN_ERR_INVALID_ARG, "cache append: batch %d, row of %d elements (multiple of 8), capacity %lld", batch,
+                row_elems, static_cast<long long>(capacity));
+  if (cache_seq_stride % 8 || cache_row_stride % 8 || new_seq_stride % 8 || cache_row_stride < row_elems ||
+      ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(k_new) |
+        reinterpret_cast<uintptr_t>(v_new)) & 15))
+    return fail(SQATTN_ERR_INVALID_ARG, "cache append: pointers need 16-byte alignment, strides multiples of 8 elements");
+  const int grid = elementwise_grid(2ll * batch * (row_elems / 8), 256);
+  cache_append_kernel<<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache),
+                                                static_cast<const uint8_t*>(k_new), static_cast<const uint8_t*>(v_new),
+                                                reinterpret_cast<const long long*>(positions), cache_seq_stride,
+                                                cache_row_stride, new_seq_stride, batch, row_elems, capacity);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
 // ---- diagnostics -----------------------------------------------------------------------------------------
 int sqattn_check_device_status(sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -854,7 +898,19 @@ int sqattn_check_device_status(sqattn_stream_t stream_) {
   return SQATTN_OK;
 }
 
+int sqattn_set_status_mirror(int32_t* host_word) {
+  int* dev_view = nullptr;
+  if (host_word) {
+    cudaError_t e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_view), host_word, 0);
+    if (e != cudaSuccess || !dev_view)
+      return fail(SQATTN_ERR_INVALID_ARG, "status mirror: the word must be pinned, device-mapped host memory (%s)",
+                  cudaGetErrorString(e));
+  }
+  SQ_CUDA(cudaMemcpyToSymbol(g_status_mirror, &dev_view, sizeof(dev_view)));
+  return SQATTN_OK;
+}
+
 const char* sqattn_last_error_string(void) { return err_buf(); }
-int sqattn_version(void) { return 100; }
+int sqattn_version(void) { return 110; }
 
 }  // extern "C"

@@ -44,6 +44,30 @@ def _shape(t: torch.Tensor, layout: str):
     return (b, x, y, d) if layout == "HND" else (b, y, x, d)
 
 
+_MIRRORS = {}
+
+
+def poll_device_status(device=None):
+    """Cheap, non-synchronising look at the failure word of ``device``: a pinned host int32 that a kernel whose bounded
+    wait gave up also writes to (sqattn_set_status_mirror).  Raises SqattnError(ERR_DEVICE_TIMEOUT) once a failure has
+    become visible; every operator below calls it on entry, so a caller of the drop-in operator hears about a timed-out
+    wait at its next call at the latest (and meanwhile gets NaN, never stale memory).  The device-side word stays set,
+    and later launches keep returning NaN, until ``check_device_status`` has cleared it."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    ent = _MIRRORS.get(idx)
+    if ent is None:
+        if torch.cuda.is_current_stream_capturing():
+            return
+        word = torch.zeros(1, dtype=torch.int32).pin_memory()
+        with torch.cuda.device(idx):
+            L.check(L.lib.sqattn_set_status_mirror(word.data_ptr()))
+        ent = _MIRRORS[idx] = (word, C.c_int32.from_address(word.data_ptr()))
+    code = ent[1].value
+    if code:
+        raise L.SqattnError(L.ERR_DEVICE_TIMEOUT, f"a device-side wait gave up on cuda:{idx} (code {code}: 1xx prefill, "
+                            "2xx decode, 3xx peer exchange); outputs since then are NaN; call check_device_status() to clear")
+
+
 def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
     if nbytes == 0:
         return None
@@ -55,10 +79,12 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
 def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0, layout: str = "HND",
             out_dtype=torch.float16, return_lse: bool = False, p_fp8_mode: int = 0, q_is_scaled: bool = False,
             out: Optional[torch.Tensor] = None, out_layout: Optional[str] = None, kv_layout: Optional[str] = None,
-            q_row_offset: int = 0):
+            q_row_offset: int = 0, head_dim_og: int = 0, q_split_rows: int = 0, q_row_offset2: int = 0):
     """sqattn_prefill.  win8/win4: per-head sequences (floats for the relative mode, ints for the absolute).
-    kv_layout: layout of k/v when it differs from q's; q_row_offset: first row of a query shard."""
+    kv_layout: layout of k/v when it differs from q's; q_row_offset: first row of a query shard; head_dim_og: the
+    head_dim before the caller zero-padded the tensors to 64 / 128 (the softmax scale follows it)."""
     _require_cuda(q8, k8, q4, k4, v)
+    poll_device_status(q8.device)
     b, hq, n, d = _shape(q8, layout)
     kv_layout = kv_layout or layout
     _, hkv, kv_len, _ = _shape(k8, kv_layout)
@@ -70,7 +96,8 @@ def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0
     a.q_int8, a.k_int8 = _view(q8, layout), _view(k8, kv_layout)
     a.q_int4, a.k_int4 = _view(q4, layout), _view(k4, kv_layout)
     a.v, a.o = _view(v, kv_layout), _view(out, out_layout)
-    a.q_row_offset = int(q_row_offset)
+    a.q_row_offset, a.head_dim_og = int(q_row_offset), int(head_dim_og)
+    a.q_split_rows, a.q_row_offset2 = int(q_split_rows), int(q_row_offset2)   # second row range of a shard, if any
     a.lse = lse.data_ptr() if lse is not None else None
     a.batch, a.num_q_heads, a.num_kv_heads, a.qo_len, a.kv_len, a.head_dim = b, hq, hkv, n, kv_len, d
     a.qk_dtype, a.v_dtype, a.o_dtype = _dt(q8.dtype), _dt(v.dtype), _dt(out.dtype)
@@ -162,7 +189,7 @@ def k_column_sums(key: torch.Tensor) -> torch.Tensor:
 def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse: bool = False, p_fp8: bool = False,
            q_is_scaled: bool = False, kv_lens: Optional[Sequence[int]] = None, kv_len: Optional[int] = None,
            num_splits: int = 0, partial: bool = False, reference_tail: bool = False,
-           kv_lens_device: Optional[torch.Tensor] = None, peer=None):
+           kv_lens_device: Optional[torch.Tensor] = None, peer=None, head_dim_og: int = 0):
     """sqattn_decode.  q [B,Hq,1,D] (HND) or [B,1,Hq,D] (NHD); k/v caches of capacity >= kv_len.
     partial=True returns (O fp32 [B,Hq,D], LSE fp32 [B,Hq]) of these keys for a later merge.
     reference_tail=True reproduces the reference kernel's zero-score padding of the last 64-key tile.
@@ -172,12 +199,13 @@ def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse:
     exchange with the other GPUs and the merge across GPUs happen in one kernel; returns nothing (the result is
     written to peer.out)."""
     _require_cuda(q, k, v)
+    poll_device_status(q.device)
     b, hq, one, d = _shape(q, layout)
     assert one == 1
     _, hkv, cap, _ = _shape(k, layout)
     a = L.DecodeArgs()
     a.q, a.k, a.v = _view(q, layout), _view(k, layout), _view(v, layout)
-    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = b, hq, hkv, d
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim, a.head_dim_og = b, hq, hkv, d, int(head_dim_og)
     a.kv_len = int(cap if kv_len is None else kv_len)
     lens = None
     if kv_lens is not None:
@@ -233,8 +261,14 @@ def decode_merge(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype=torch.f
 
 
 def check_device_status():
-    """Raise if a bounded device-side wait gave up since the last check (synchronises the stream)."""
-    L.check(L.lib.sqattn_check_device_status(_stream()))
+    """Raise if a bounded device-side wait gave up since the last check (synchronises the stream); clears the
+    device word and its host mirror, after which launches compute again."""
+    ent = _MIRRORS.get(torch.cuda.current_device())
+    try:
+        L.check(L.lib.sqattn_check_device_status(_stream()))
+    finally:
+        if ent is not None:
+            ent[1].value = 0
 
 
 def decode_static_scratch(q, k, v, out, *, layout: str = "HND", lse: Optional[torch.Tensor] = None,

@@ -34,10 +34,11 @@ def _per_head(w, h, conv):
     return w
 
 
-def _unscale_note():
-    # q is scaled inside the library (q_is_scaled=False) exactly as the reference launchers do before the
-    # kernel call; callers that already scaled q use the C ABI / ops.prefill directly.
-    return False
+def _slice_back(res, d_og):
+    """o[..., :head_dim_og] (attn_triton.py:314); the LSE has no head_dim axis."""
+    if isinstance(res, tuple):
+        return (res[0] if res[0].shape[-1] == d_og else res[0][..., :d_og], res[1])
+    return res if res.shape[-1] == d_og else res[..., :d_og]
 
 
 def attn_hierarchical_relative_window(q_int8, k_int8, q_int4, k_int4, v, int8_window_ratios, int4_window_ratios,
@@ -48,8 +49,6 @@ def attn_hierarchical_relative_window(q_int8, k_int8, q_int4, k_int4, v, int8_wi
     if not isinstance(sink_size, int) or sink_size < 0:
         raise ValueError(f"sink_size must be a non-negative integer, got {sink_size}")
     (q_int8, k_int8, q_int4, k_int4, v), d_og = _pad_head_dim([q_int8, k_int8, q_int4, k_int4, v])
-    if d_og != q_int8.shape[-1]:
-        raise ValueError("head_dim padding changes the softmax scale: pass head_dim 64 or 128")
     h = q_int8.shape[1] if tensor_layout == "HND" else q_int8.shape[2]
     r8 = _per_head(int8_window_ratios, h, float)
     r4 = _per_head(int4_window_ratios, h, float)
@@ -58,9 +57,10 @@ def attn_hierarchical_relative_window(q_int8, k_int8, q_int4, k_int4, v, int8_wi
     mode = L.P_FP8_ALL if is_P_fp8_quant else L.P_FP8_OFF
     if p_fp8_mode is not None:
         mode = {"off": L.P_FP8_OFF, "all": L.P_FP8_ALL, "stage2": L.P_FP8_STAGE2}[p_fp8_mode]
-    return ops.prefill(q_int8, k_int8, q_int4, k_int4, v, mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4,
-                       sink=sink_size, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
-                       p_fp8_mode=mode, q_is_scaled=_unscale_note())
+    # q is scaled inside the library (q_is_scaled=False), as the reference launchers do before the kernel call
+    return _slice_back(ops.prefill(q_int8, k_int8, q_int4, k_int4, v, mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4,
+                                   sink=sink_size, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
+                                   p_fp8_mode=mode, q_is_scaled=False, head_dim_og=d_og), d_og)
 
 
 def attn_hierarchical_window(q_int8, k_int8, q_int4, k_int4, v, int8_window_sizes, int4_window_sizes, sink_size,
@@ -70,26 +70,23 @@ def attn_hierarchical_window(q_int8, k_int8, q_int4, k_int4, v, int8_window_size
     if not isinstance(sink_size, int) or sink_size < 0:
         raise ValueError(f"sink_size must be a non-negative integer, got {sink_size}")
     (q_int8, k_int8, q_int4, k_int4, v), d_og = _pad_head_dim([q_int8, k_int8, q_int4, k_int4, v])
-    if d_og != q_int8.shape[-1]:
-        raise ValueError("head_dim padding changes the softmax scale: pass head_dim 64 or 128")
     h = q_int8.shape[1] if tensor_layout == "HND" else q_int8.shape[2]
     s8 = _per_head(int8_window_sizes, h, int)
     s4 = _per_head(int4_window_sizes, h, int)
-    return ops.prefill(q_int8, k_int8, q_int4, k_int4, v, mode=L.MODE_ABSOLUTE_WINDOW, win8=s8, win4=s4,
-                       sink=sink_size, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
-                       p_fp8_mode=L.P_FP8_ALL if is_P_fp8_quant else L.P_FP8_OFF, q_is_scaled=False)
+    return _slice_back(ops.prefill(q_int8, k_int8, q_int4, k_int4, v, mode=L.MODE_ABSOLUTE_WINDOW, win8=s8, win4=s4,
+                                   sink=sink_size, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
+                                   p_fp8_mode=L.P_FP8_ALL if is_P_fp8_quant else L.P_FP8_OFF, q_is_scaled=False,
+                                   head_dim_og=d_og), d_og)
 
 
 def attn_causal(q, k, v, tensor_layout="HND", output_dtype=torch.float16, return_lse=False, is_P_fp8_quant=False):
     """Dense causal GQA attention."""
     (q, k, v), d_og = _pad_head_dim([q, k, v])
-    if d_og != q.shape[-1]:
-        raise ValueError("head_dim padding changes the softmax scale: pass head_dim 64 or 128")
     seq_dim = 1 if tensor_layout == "NHD" else 2
     assert q.shape[seq_dim] == k.shape[seq_dim], "qo_len and kv_len must be equal for causal attention"
-    return ops.prefill(q, k, q, k, v, mode=L.MODE_DENSE_CAUSAL, layout=tensor_layout, out_dtype=output_dtype,
-                       return_lse=return_lse, p_fp8_mode=L.P_FP8_ALL if is_P_fp8_quant else L.P_FP8_OFF,
-                       q_is_scaled=False)
+    return _slice_back(ops.prefill(q, k, q, k, v, mode=L.MODE_DENSE_CAUSAL, layout=tensor_layout, out_dtype=output_dtype,
+                                   return_lse=return_lse, p_fp8_mode=L.P_FP8_ALL if is_P_fp8_quant else L.P_FP8_OFF,
+                                   q_is_scaled=False, head_dim_og=d_og), d_og)
 
 
 def attn_unified(q, k, v, tensor_layout="HND", output_dtype=torch.float16, return_lse=False, is_P_fp8_quant=False,
@@ -102,6 +99,7 @@ def attn_unified(q, k, v, tensor_layout="HND", output_dtype=torch.float16, retur
         km = k.float().mean(dim=seq_dim, keepdim=True).to(k.dtype)
         k = k - km
     if q.shape[seq_dim] == 1:
-        return ops.decode(q, k, v, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
-                          p_fp8=is_P_fp8_quant, kv_lens=kv_lens, reference_tail=True)
+        (qp, kp, vp), d_og = _pad_head_dim([q, k, v])
+        return _slice_back(ops.decode(qp, kp, vp, layout=tensor_layout, out_dtype=output_dtype, return_lse=return_lse,
+                                      p_fp8=is_P_fp8_quant, kv_lens=kv_lens, reference_tail=True, head_dim_og=d_og), d_og)
     return attn_causal(q, k, v, tensor_layout, output_dtype, return_lse, is_P_fp8_quant)
