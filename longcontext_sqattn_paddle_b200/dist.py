@@ -3,25 +3,31 @@
 The reference has no multi-GPU path beyond layer-to-device placement (model_hub/qwen.py:203-267); these are the
 two places where the path shards naturally:
 
-* prefill: query rows are independent given K and V.  Rank r owns the tokens
-  [r*Ns, (r+1)*Ns) of a sequence of world*Ns tokens.  Exchange steps: an all-reduce of the K column sums
-  [B,Hkv,D] fp32 (the sequence mean that the adapter subtracts, sqattn/attn_replacer.py:338-339, is global)
-  and an all-gather of the prepared K and V shards, written token-major so the gathered tensor is contiguous.
-  Per-token Q/K scales and per-(token,channel) V scales are local to a shard.  The attention kernel then runs
-  on the local query rows with q_row_offset = r*Ns against the gathered K/V in local memory.
+* prefill: query rows are independent given K and V.  A ``ShardLayout`` says which token ranges of the sequence a
+  rank owns: equal contiguous shards, contiguous shards cut so that the windowed attention work is equal
+  (``balanced``), or the zig-zag split (rank r owns chunks r and 2G-1-r of 2G equal chunks) that balances dense
+  causal work.  Exchange steps of a windowed layer: an all-reduce of the K column sums [B,Hkv,D] fp32 (the
+  sequence mean that the adapter subtracts, sqattn/attn_replacer.py:338-339, is global) and a HALO exchange of
+  the prepared K and V rows: a rank only needs the sink tokens and the ``reach`` (largest window) tokens in front
+  of each of its row ranges, 13 440 tokens instead of 131 072 at the reference's default window, sent point to
+  point.  The all-reduce runs while V is prepared and the halo exchange while Q is prepared, so neither is on
+  the critical path.  A dense causal layer (the un-replaced first and last layer, model_hub/qwen.py:38-48)
+  all-gathers the raw K and V.  Per-token Q/K scales and per-(token,channel) V scales are local to a shard.  The
+  attention kernel then runs on the local query rows (one launch, one or two row ranges) against K/V in local
+  memory; it never reads a peer's memory.
 * decode: the cache is sharded by key ranges; every rank computes (partial O, LSE) over its keys, one
   all-gather of [B*Hq, D+1] floats, one merge kernel.
 
-The collectives go through ``torch.distributed`` (NCCL on GPUs) and the attention kernels only ever read local
-memory.  For decode, where the exchange is 14 KB per rank and latency is everything, ``PeerExchange`` replaces
-the all-gather + merge by ONE kernel that stores the partials into every rank's buffer over NVLink (plain peer
-stores into symmetric memory), flags, waits and merges (csrc/peer_exchange.cuh).
+The collectives go through ``torch.distributed`` (NCCL on GPUs).  For decode, where the exchange is 14 KB per rank
+and latency is everything, ``PeerExchange`` replaces the all-gather + merge by ONE kernel that stores the partials
+into every rank's buffer over NVLink (plain peer stores into symmetric memory), flags, waits and merges
+(csrc/peer_exchange.cuh).
 The compute steps are taken from a ``backend`` object so that the partitioning logic can be exercised on CPU
 ranks (gloo) with a stand-in backend; the default backend is the CUDA library and nothing else ships.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -32,6 +38,124 @@ import os
 from . import _lib as L
 
 
+# ------------------------------------------------------------------------------------------- shard layouts
+class ShardLayout:
+    """Token ranges of a ``total``-token sequence owned by each of ``world`` ranks.  ``segments(rank)`` lists the
+    rank's ranges [(lo, hi), ...] (one or two) in the order its local rows are stored; every range starts on a
+    multiple of 128 rows and ends on one unless it ends the sequence."""
+
+    def __init__(self, total: int, world: int, segments: List[List[Tuple[int, int]]], kind: str):
+        self.total, self.world, self._segs, self.kind = int(total), int(world), segments, kind
+        covered = sorted(s for segs in segments for s in segs)
+        pos = 0
+        for lo, hi in covered:
+            if lo != pos or hi <= lo:
+                raise ValueError(f"shard layout does not tile the sequence: {covered}")
+            if lo % 128 or (hi % 128 and hi != total):
+                raise ValueError(f"row range [{lo}, {hi}) is not aligned to 128 rows")
+            pos = hi
+        if pos != total:
+            raise ValueError(f"shard layout covers {pos} of {total} tokens")
+        if any(len(s) > 2 for s in segments):
+            raise ValueError("at most two row ranges per rank")
+
+    def segments(self, rank: int) -> List[Tuple[int, int]]:
+        return list(self._segs[rank])
+
+    def rows(self, rank: int) -> int:
+        return sum(hi - lo for lo, hi in self._segs[rank])
+
+    def owner_of_last_token(self) -> int:
+        return next(r for r in range(self.world) if any(hi == self.total for _, hi in self._segs[r]))
+
+    @classmethod
+    def contiguous(cls, total: int, world: int) -> "ShardLayout":
+        if total % world:
+            raise ValueError(f"sequence length {total} is not divisible by the world size {world}")
+        ns = total // world
+        if world > 1 and ns % 128:
+            raise ValueError(f"shard length {ns} must be a multiple of 128 query rows")
+        return cls(total, world, [[(r * ns, (r + 1) * ns)] for r in range(world)], "contiguous")
+
+    @classmethod
+    def zigzag(cls, total: int, world: int) -> "ShardLayout":
+        """Rank r owns chunks r and 2G-1-r of 2G equal chunks: under a causal mask the cheap early rows and the
+        expensive late rows pair up, so every rank has the same dense-attention work."""
+        if world == 1:
+            return cls.contiguous(total, 1)
+        if total % (2 * world) or (total // (2 * world)) % 128:
+            raise ValueError(f"zig-zag sharding needs {total} tokens to split into {2 * world} chunks of a multiple of 128")
+        c = total // (2 * world)
+        return cls(total, world, [[(r * c, (r + 1) * c), ((2 * world - 1 - r) * c, (2 * world - r) * c)]
+                                  for r in range(world)], "zigzag")
+
+    @classmethod
+    def balanced(cls, total: int, world: int, reach: int, sink: int) -> "ShardLayout":
+        """Contiguous shards whose WINDOWED attention work is equal: a row attends to at most sink + reach + its
+        diagonal block, the first rows to fewer, so the first rank takes more rows.  Cuts are multiples of 128."""
+        nblk = (total + 127) // 128
+        cost, acc = [], 0
+        for b in range(nblk):
+            qs = b * 128
+            acc += min(sink, qs) + min(max(qs + 64 - sink, 0), reach) + 64
+            cost.append(acc)
+        cuts, b = [0], 0
+        for r in range(1, world):
+            target = acc * r / world
+            while b < nblk and cost[b] < target:
+                b += 1
+            cuts.append(min(max(b + 1, cuts[-1] // 128 + 1), nblk - (world - r)) * 128)
+        cuts.append(total)
+        if any(cuts[i + 1] <= cuts[i] for i in range(world)):
+            raise ValueError(f"{total} tokens are too few for {world} balanced shards")
+        return cls(total, world, [[(cuts[r], cuts[r + 1])] for r in range(world)], "balanced")
+
+
+def shard_range(rank: int, world: int, seq_total: int):
+    """Token range [lo, hi) owned by ``rank`` under equal contiguous shards, each a multiple of 128 rows."""
+    return ShardLayout.contiguous(seq_total, world).segments(rank)[0]
+
+
+def halo_plan(layout: ShardLayout, reach: int, sink: int) -> List[Tuple[int, int, int, int]]:
+    """Point-to-point transfers (src, dst, lo, hi) of key/value rows so that every rank holds, besides its own
+    rows, the sink tokens [0, sink) and the ``reach`` tokens in front of each of its row ranges.  The same list is
+    computed on every rank; ranges are cut at ownership boundaries."""
+    owned = [(lo, hi, r) for r in range(layout.world) for lo, hi in layout.segments(r)]
+    plan = []
+    for dst in range(layout.world):
+        need = []
+        for lo, hi in layout.segments(dst):
+            if sink > 0:
+                need.append((0, min(sink, layout.total)))
+            if reach > 0 and lo > 0:
+                need.append((max(0, lo - reach), lo))
+        need.sort()
+        merged = []
+        for lo, hi in need:                       # union of the needed ranges
+            if merged and lo <= merged[-1][1]:
+                merged[-1] = (merged[-1][0], max(merged[-1][1], hi))
+            else:
+                merged.append((lo, hi))
+        for nlo, nhi in merged:
+            for olo, ohi, src in owned:
+                lo, hi = max(nlo, olo), min(nhi, ohi)
+                if lo < hi and src != dst:
+                    plan.append((src, dst, lo, hi))
+    plan.sort()
+    return plan
+
+
+def _local_rows(segs: List[Tuple[int, int]], lo: int, hi: int) -> Tuple[int, int]:
+    """Local row range of the global rows [lo, hi), which lie inside one of the rank's ranges."""
+    base = 0
+    for slo, shi in segs:
+        if slo <= lo and hi <= shi:
+            return base + lo - slo, base + hi - slo
+        base += shi - slo
+    raise ValueError(f"rows [{lo}, {hi}) are not owned by this rank")
+
+
+# ------------------------------------------------------------------------------------------- compute backend
 class CudaBackend:
     """The compute steps on the local GPU (libsqattn_b200.so)."""
 
@@ -39,19 +163,46 @@ class CudaBackend:
         from . import ops
         return ops.k_column_sums(key)
 
-    def prep(self, query, key, value, k_mean, qk_qtype, v_qtype):
-        from . import ops
-        q8, _, k8, _, v8 = ops.prep_qkv(query, key, value, qk_qtype=qk_qtype, v_qtype=v_qtype, skip_bit4=True,
-                                        k_mean=k_mean, kv_out_nhd=True)
-        return q8, k8, v8
+    def empty_kv(self, total, hkv, d, dtype, like):
+        return torch.empty(1, total, hkv, d, dtype=dtype, device=like.device)
 
-    def windowed_prefill(self, q8, k_full, v_full, win8, win4, sink, q_row_offset, p_fp8_mode):
+    def prep_q(self, query, qk_qtype, need_bit4):
+        """query [1,ns,Hq,D] -> (q_bit8, q_bit4 or None) [1,Hq,ns,D], already scaled."""
+        from . import ops
+        q8, q4, _, _, _ = ops.prep_qkv(query, None, None, qk_qtype=qk_qtype, skip_bit4=not need_bit4)
+        return q8, q4
+
+    def prep_k(self, key, k_mean, qk_qtype, out8, out4):
+        """key [1,n,Hkv,D] minus the global mean, fake-quantised into the token-major views out8 (and out4)."""
+        from . import ops
+        ops.prep_qkv(None, key, None, qk_qtype=qk_qtype, skip_bit4=out4 is None, k_mean=k_mean, kv_out_nhd=True,
+                     out={"k8": out8, "k4": out4})
+
+    def prep_v(self, value, v_qtype, out):
+        from . import ops
+        ops.prep_qkv(None, None, value, v_qtype=v_qtype, skip_bit4=True, kv_out_nhd=True, out={"v8": out})
+
+    def _segs(self, segs):
+        if len(segs) == 1:
+            return dict(q_row_offset=segs[0][0])
+        return dict(q_row_offset=segs[0][0], q_split_rows=segs[0][1] - segs[0][0], q_row_offset2=segs[1][0])
+
+    def windowed_prefill(self, q8, q4, k8, k4, v_full, win8, win4, sink, segs, relative, p_fp8_mode):
         from . import ops
         b, hq, n, d = q8.shape
         out = torch.empty(b, n, hq * d, dtype=torch.bfloat16, device=q8.device)
-        ops.prefill(q8, k_full, q8, k_full, v_full, mode=L.MODE_RELATIVE_WINDOW, win8=win8, win4=win4, sink=sink,
+        ops.prefill(q8, k8, q8 if q4 is None else q4, k8 if k4 is None else k4, v_full,
+                    mode=L.MODE_RELATIVE_WINDOW if relative else L.MODE_ABSOLUTE_WINDOW, win8=win8, win4=win4, sink=sink,
                     layout="HND", kv_layout="NHD", p_fp8_mode=p_fp8_mode, q_is_scaled=True,
-                    out=out.view(b, n, hq, d), out_layout="NHD", q_row_offset=q_row_offset)
+                    out=out.view(b, n, hq, d), out_layout="NHD", **self._segs(segs))
+        return out
+
+    def dense_prefill(self, query, k_full, v_full, segs):
+        from . import ops
+        b, n, hq, d = query.shape
+        out = torch.empty(b, n, hq * d, dtype=query.dtype, device=query.device)
+        ops.prefill(query, k_full, query, k_full, v_full, mode=L.MODE_DENSE_CAUSAL, layout="NHD", q_is_scaled=False,
+                    out=out.view(b, n, hq, d), out_layout="NHD", **self._segs(segs))
         return out
 
     def decode_partial(self, q, k, v, kv_lens, p_fp8):
@@ -131,22 +282,54 @@ class PeerExchange:
         return out.view(b, hq, 1, d)
 
 
-def shard_range(rank: int, world: int, seq_total: int):
-    """Token range [lo, hi) owned by ``rank``: equal contiguous shards, each a multiple of 128 rows."""
-    if seq_total % world:
-        raise ValueError(f"sequence length {seq_total} is not divisible by the world size {world}")
-    ns = seq_total // world
-    if world > 1 and ns % 128:
-        raise ValueError(f"shard length {ns} must be a multiple of 128 query rows")
-    return rank * ns, (rank + 1) * ns
+# ------------------------------------------------------------------------------------------- prefill
+def _group_info(group):
+    if dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+def _global_rank(group, r):
+    return r if group is None else dist.get_global_rank(group, r)
+
+
+def _resolve_layout(layout, total, world, reach, sink) -> ShardLayout:
+    if isinstance(layout, ShardLayout):
+        if layout.total != total or layout.world != world:
+            raise ValueError(f"layout describes {layout.total} tokens on {layout.world} ranks, call has {total} on {world}")
+        return layout
+    if layout == "contiguous":
+        return ShardLayout.contiguous(total, world)
+    if layout == "zigzag":
+        return ShardLayout.zigzag(total, world)
+    if layout == "balanced":
+        return ShardLayout.balanced(total, world, reach, sink)
+    raise ValueError(f"unknown shard layout {layout!r}")
+
+
+def _per_head(w, hq, conv):
+    return [conv(w)] * hq if isinstance(w, (int, float)) else [conv(x) for x in w]
+
+
+def _window_reach(win8, win4, relative, total) -> int:
+    """Largest distance (in tokens) a query row looks back beyond its own 128-row block."""
+    if relative:
+        def size(r):
+            raw = int((torch.tensor(r, dtype=torch.float32) * torch.tensor(float(total), dtype=torch.float32)).item())
+            return (raw + 127) // 128 * 128
+        return max(max(size(r) for r in win8), max(size(r) for r in win4), 0)
+    return max(max(int(x) for x in win8), max(int(x) for x in win4), 0)
 
 
 def sp_prefill_wrapper(bit8_window_sizes, bit4_window_sizes, sink_window_size, args, seq_total: Optional[int] = None,
-                       group=None, backend=None, p_fp8_mode: int = 0):
-    """Sequence-parallel counterpart of ``mp_triton_wrapper`` (relative windows): returns
-    attention_fn(module, query, key, value, attention_mask, ...) where query/key/value are THIS rank's token
-    shard ([B=1, Ns, H, D]) and the result is this rank's [1, Ns, Hq*D] slice of the output."""
+                       group=None, backend=None, p_fp8_mode: int = 0, layout="contiguous", exchange: str = "halo"):
+    """Sequence-parallel counterpart of ``mp_triton_wrapper`` (relative or absolute windows): returns
+    attention_fn(module, query, key, value, attention_mask, ...) where query/key/value are THIS rank's token rows
+    ([B=1, ns, H, D], its row ranges in ``layout`` order) and the result is this rank's [1, ns, Hq*D] rows of the
+    output.  ``exchange``: "halo" sends every rank only the sink and window rows it needs, "allgather" gathers all
+    prepared K/V (equal shards only)."""
     backend = backend or CudaBackend()
+    state = {}
 
     def attention_fn(module, query, key, value, attention_mask=None, dropout=0.0, scaling=1.0, sliding_window=None,
                      **kwargs):
@@ -154,41 +337,124 @@ def sp_prefill_wrapper(bit8_window_sizes, bit4_window_sizes, sink_window_size, a
             raise ValueError(f"Invalid quantization type: {args.qk_qtype}")
         if args.v_qtype not in L.QTYPE:
             raise ValueError(f"Invalid quantization type: {args.v_qtype}")
-        if not args.use_relative_distance:
-            raise ValueError("sequence-parallel prefill is implemented for relative windows")
-        world = dist.get_world_size(group) if dist.is_initialized() else 1
-        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        relative = bool(args.use_relative_distance)
+        world, rank = _group_info(group)
         b, ns, hq, d = query.shape
         hkv = key.shape[2]
         if b != 1:
             raise ValueError("sequence-parallel prefill takes one sequence (batch 1), like the reference's cache")
         total = seq_total if seq_total is not None else ns * world
-        lo, hi = shard_range(rank, world, total)
-        if hi - lo != ns:
-            raise ValueError(f"rank {rank} holds {ns} tokens, expected {hi - lo}")
-        # global sequence mean of K: all-reduce the shards' column sums (2 KB), divide once
+        win8 = _per_head(bit8_window_sizes, hq, float if relative else int)
+        win4 = _per_head(bit4_window_sizes, hq, float if relative else int)
+        key_ = (total, world, hkv, d, key.dtype, key.device)
+        if state.get("key") != key_:
+            reach = _window_reach(win8, win4, relative, total)
+            lay = _resolve_layout(layout, total, world, reach, sink_window_size)
+            # a stage's 64-key tiles may run up to 63 keys past its end, as in the reference loops: the sink rounds up
+            state.update(key=key_, layout=lay, plan=halo_plan(lay, reach, (sink_window_size + 63) // 64 * 64),
+                         k8=backend.empty_kv(total, hkv, d, key.dtype, key),
+                         k4=None if relative else backend.empty_kv(total, hkv, d, key.dtype, key),
+                         v8=backend.empty_kv(total, hkv, d, torch.float16, key))
+        lay, k8, k4, v8 = state["layout"], state["k8"], state["k4"], state["v8"]
+        segs = lay.segments(rank)
+        if lay.rows(rank) != ns:
+            raise ValueError(f"rank {rank} holds {ns} tokens, its shard has {lay.rows(rank)}")
+        # 1. global sequence mean of K: all-reduce of the shards' column sums (2 KB) while V is prepared
         sums = backend.k_column_sums(key)
-        if world > 1:
-            dist.all_reduce(sums, group=group)
+        work = dist.all_reduce(sums, group=group, async_op=True) if world > 1 else None
+        base = 0
+        for lo, hi in segs:
+            backend.prep_v(value[:, base:base + hi - lo], args.v_qtype, v8[:, lo:hi])
+            base += hi - lo
+        if work is not None:
+            work.wait()
         k_mean = (sums / float(total)).contiguous()
-        q8, k8, v8 = backend.prep(query, key, value, k_mean, args.qk_qtype, args.v_qtype)  # k8/v8 [1,Ns,Hkv,D]
-        if world > 1:
-            k_full = torch.empty(1, total, hkv, d, dtype=k8.dtype, device=k8.device)
-            v_full = torch.empty(1, total, hkv, d, dtype=v8.dtype, device=v8.device)
-            dist.all_gather_into_tensor(k_full.view(total, hkv, d), k8.view(ns, hkv, d), group=group)
-            dist.all_gather_into_tensor(v_full.view(total, hkv, d), v8.view(ns, hkv, d), group=group)
-        else:
-            k_full, v_full = k8, v8
+        base = 0
+        for lo, hi in segs:
+            backend.prep_k(key[:, base:base + hi - lo], k_mean, args.qk_qtype, k8[:, lo:hi],
+                           None if k4 is None else k4[:, lo:hi])
+            base += hi - lo
+        # 2. the rows other ranks need travel while Q is prepared
+        works = []
+        if world > 1 and exchange == "halo":
+            p2p = []
+            for src, dst, lo, hi in state["plan"]:
+                for buf in (k8, k4, v8):
+                    if buf is None:
+                        continue
+                    if src == rank:
+                        p2p.append(dist.P2POp(dist.isend, buf[0, lo:hi], _global_rank(group, dst), group))
+                    elif dst == rank:
+                        p2p.append(dist.P2POp(dist.irecv, buf[0, lo:hi], _global_rank(group, src), group))
+            if p2p:
+                works = dist.batch_isend_irecv(p2p)
+        elif world > 1:
+            if lay.kind != "contiguous":
+                raise ValueError("exchange='allgather' needs equal contiguous shards")
+            lo, hi = segs[0]
+            for buf in (k8, k4, v8):
+                if buf is not None:
+                    mine = buf[0, lo:hi].clone()
+                    works.append(dist.all_gather_into_tensor(buf.view(total, hkv, d), mine, group=group, async_op=True))
+        q8, q4 = backend.prep_q(query, args.qk_qtype, not relative)
+        for w in works:
+            w.wait()
+        return backend.windowed_prefill(q8, q4, k8, k4, v8, win8, win4, sink_window_size, segs, relative, p_fp8_mode)
 
-        def per_head(w):
-            return [float(w)] * hq if isinstance(w, (int, float)) else [float(x) for x in w]
-
-        return backend.windowed_prefill(q8, k_full, v_full, per_head(bit8_window_sizes), per_head(bit4_window_sizes),
-                                        sink_window_size, lo, p_fp8_mode)
-
+    attention_fn.state = state
     return attention_fn
 
 
+def sp_dense_wrapper(seq_total: Optional[int] = None, group=None, backend=None, layout="zigzag"):
+    """Sequence-parallel dense causal attention for the layers the reference leaves un-replaced
+    (model_hub/qwen.py:38-48; its first and last layer, sqattn/compress.py:162): the raw K and V shards are
+    all-gathered into sequence order and every rank attends its own rows (``layout``: "zigzag" balances the causal
+    work, "contiguous" does not).  Same calling convention as ``sp_prefill_wrapper``; output in the input dtype."""
+    backend = backend or CudaBackend()
+    state = {}
+
+    def attention_fn(module, query, key, value, attention_mask=None, dropout=0.0, scaling=1.0, sliding_window=None,
+                     **kwargs):
+        world, rank = _group_info(group)
+        b, ns, hq, d = query.shape
+        hkv = key.shape[2]
+        if b != 1:
+            raise ValueError("sequence-parallel prefill takes one sequence (batch 1), like the reference's cache")
+        total = seq_total if seq_total is not None else ns * world
+        key_ = (total, world, hkv, d, key.dtype, key.device)
+        if state.get("key") != key_:
+            lay = _resolve_layout(layout, total, world, 0, 0)
+            if lay.kind not in ("contiguous", "zigzag"):
+                raise ValueError("dense sequence-parallel attention needs equal shards (contiguous or zig-zag)")
+            state.update(key=key_, layout=lay, k=backend.empty_kv(total, hkv, d, key.dtype, key),
+                         v=backend.empty_kv(total, hkv, d, value.dtype, key))
+        lay, k_full, v_full = state["layout"], state["k"], state["v"]
+        segs = lay.segments(rank)
+        if lay.rows(rank) != ns:
+            raise ValueError(f"rank {rank} holds {ns} tokens, its shard has {lay.rows(rank)}")
+        if world == 1:
+            return backend.dense_prefill(query, key, value, segs)
+        works = []
+        for full, mine in ((k_full, key), (v_full, value)):
+            if lay.kind == "contiguous":
+                works.append(dist.all_gather_into_tensor(full.view(total, hkv, d), mine[0].contiguous(), group=group,
+                                                         async_op=True))
+            else:
+                c = ns // 2
+                # first halves are chunks 0..G-1 in rank order; second halves are chunks 2G-1..G
+                works.append(dist.all_gather_into_tensor(full[0, :total // 2], mine[0, :c].contiguous(), group=group,
+                                                         async_op=True))
+                outs = [full[0, (2 * world - 1 - r) * c:(2 * world - r) * c] for r in range(world)]
+                works.append(dist.all_gather(outs, mine[0, c:].contiguous(), group=group, async_op=True))
+        for w in works:
+            w.wait()
+        return backend.dense_prefill(query, k_full, v_full, segs)
+
+    attention_fn.state = state
+    return attention_fn
+
+
+# ------------------------------------------------------------------------------------------- decode
 def sp_decode(q, k_shard, v_shard, *, kv_lens: Optional[Sequence[int]] = None, out_dtype=torch.bfloat16,
               p_fp8: bool = False, group=None, backend=None, exchange: Optional[PeerExchange] = None):
     """Split-KV decode across ranks.  q [B,Hq,1,D] (replicated), k_shard/v_shard [B,Hkv,Ls,D]: this rank's keys

@@ -5,9 +5,10 @@ with bias -> rotary embedding (YaRN past 32768 positions) -> ``layer.prefill_att
 
 Matrix products are torch (cuBLAS) calls; rmsnorm, the rotation and SiLU*up are the library's row kernels; the
 attention calls go through the same ``process_model`` / ``mp_triton_wrapper`` installation as in the reference.
-With ``seq_shard=(rank, world)`` every rank runs the layer loop on its own token shard and the attention operator
-is the sequence-parallel one (``dist.sp_prefill_wrapper``); the KV cache then holds the rank's shard of keys,
-which is the layout of the cross-GPU split-KV decode (``dist.sp_decode``).
+With ``seq_shard=(rank, world)`` every rank runs the layer loop on its own token rows (equal contiguous shards, or
+with ``shard_layout="zigzag"`` chunks r and 2G-1-r of 2G, which balances the dense causal layers) and the attention
+operators are the sequence-parallel ones (``dist.sp_prefill_wrapper`` / ``dist.sp_dense_wrapper``); the KV cache
+then holds the rank's keys, which is the layout of the cross-GPU split-KV decode (``dist.sp_decode``).
 """
 from __future__ import annotations
 
@@ -124,7 +125,7 @@ class RandomInitDecoder:
 
     def __init__(self, config: DecoderConfig, max_length: int, dtype=torch.bfloat16, device="cuda:0",
                  attention_type: str = "SQAttn", seed: int = 0, seq_shard: Tuple[int, int] = (0, 1),
-                 with_lm_head: bool = True):
+                 with_lm_head: bool = True, shard_layout: str = "contiguous"):
         self.config, self.max_length, self.dtype, self.attention_type = config, max_length, dtype, attention_type
         self.device = torch.device(device)
         self.device_map = str(device)
@@ -136,6 +137,7 @@ class RandomInitDecoder:
         self.eos_tokens = [c.eos_token_id]
         self.num_gpus = 1
         self.rank, self.world = seq_shard
+        self.shard_layout = shard_layout
         self.capture_layer_inps = None
         self.layer_mapping = {str(i): self.device_map for i in range(self.num_layers)}
         g = torch.Generator(device=self.device)
@@ -190,7 +192,16 @@ class RandomInitDecoder:
         normed = self.layernorm(hidden_states, layer.input_layernorm_variance_epsilon, layer.input_layernorm_weight)
         qkv, q, k, v = self.wqkv(normed, layer)
         del normed
-        self.position_embedd(qkv, seq_len, shard_offset=self.rank * seq_len if self.world > 1 else 0)
+        if self.world > 1:
+            # every row range of this rank's shard is rotated at its own positions in the whole sequence
+            from ..dist import ShardLayout
+            lay = getattr(ShardLayout, self.shard_layout)(seq_len * self.world, self.world)
+            base = 0
+            for lo, hi in lay.segments(self.rank):
+                self.position_embedd(qkv[:, base:base + hi - lo], hi - lo, shard_offset=lo)
+                base += hi - lo
+        else:
+            self.position_embedd(qkv, seq_len)
         query_states = q.view(bsz, seq_len, self.num_heads, self.head_dim)
         key_states = k.view(bsz, seq_len, self.num_key_value_heads, self.head_dim)
         value_states = v.view(bsz, seq_len, self.num_key_value_heads, self.head_dim)
@@ -230,8 +241,9 @@ class RandomInitDecoder:
         return residual + self.mlp(normed, layer)
 
     def prefill_forward(self, inputs_ids):
-        """inputs_ids [B, N] (this rank's token shard when sharded) -> logits [B, 1, vocab] of the last position
-        (on the last rank when sharded)."""
+        """inputs_ids [B, N] (this rank's token rows when sharded) -> logits [B, 1, vocab] of the last position
+        (when sharded: meaningful on the rank that owns the last token, the last rank for contiguous shards and
+        rank 0 for the zig-zag layout; its last local row is the last token in both)."""
         bsz, _ = inputs_ids.shape
         last_hidden_states = torch.empty(bsz, 1, self.hidden_size, dtype=self.dtype, device=self.device)
         for start_bdx in range(bsz):
@@ -340,11 +352,15 @@ class RandomInitDecoder:
 
 def install_sequence_parallel(model: RandomInitDecoder, window_sizes, args, group=None, p_fp8_mode: int = 0):
     """``process_model`` for a sharded model: every layer listed in ``window_sizes`` gets the sequence-parallel
-    operator (dist.sp_prefill_wrapper), which all-reduces the key sums and all-gathers the prepared K/V shards."""
-    from ..dist import sp_prefill_wrapper
+    windowed operator (dist.sp_prefill_wrapper: all-reduce of the key sums, halo exchange of the prepared K/V rows),
+    every other layer the sequence-parallel dense causal one (dist.sp_dense_wrapper: all-gather of K and V), both
+    on the model's shard layout."""
+    from ..dist import sp_dense_wrapper, sp_prefill_wrapper
     for i, layer in enumerate(model.layers):
         if i in window_sizes:
-            layer.prefill_attention = types.MethodType(
-                sp_prefill_wrapper(window_sizes[i]["bit8"], window_sizes[i]["bit4"], 256, args, group=group,
-                                   p_fp8_mode=p_fp8_mode), layer)
+            fn = sp_prefill_wrapper(window_sizes[i]["bit8"], window_sizes[i]["bit4"], 256, args, group=group,
+                                    p_fp8_mode=p_fp8_mode, layout=model.shard_layout)
+        else:
+            fn = sp_dense_wrapper(group=group, layout=model.shard_layout)
+        layer.prefill_attention = types.MethodType(fn, layer)
     return model
