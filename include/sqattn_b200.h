@@ -284,8 +284,10 @@ int sqattn_window_histogram(const void* q, const void* k, int32_t dtype, int32_t
  * (part_o [rows, head_dim] fp32 already divided by its own sum, part_lse [rows] fp32 base 2, as produced by
  * sqattn_decode with partial_o / partial_lse) and the device pointers of ALL ranks' exchange buffers as mapped
  * in the calling process (symmetric / IPC memory; index = rank).  The kernel stores the partial into every
- * rank's data buffer with plain peer stores, publishes a flag, waits at most one second for the other ranks
- * (then SQATTN_ERR_DEVICE_TIMEOUT is reported by sqattn_check_device_status) and writes the merged result.
+ * rank's data buffer with plain peer stores (every value as one 8-byte word that also carries the step number, so
+ * no flag or fence is needed), waits at most one second for the other ranks' words to arrive in its own buffer
+ * (then the output is NaN and SQATTN_ERR_DEVICE_TIMEOUT is reported by sqattn_check_device_status) and writes the
+ * merged result.
  * Buffers: data = sqattn_peer_merge_data_bytes(), flags = sqattn_peer_merge_flag_bytes(), zeroed once before the
  * first call.  At most 16 ranks. */
 typedef struct sqattn_peer_merge_args {

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsqattn_b200.so")
+# SQATTN_B200_LIB selects another build of the same library (e.g. the one with the debug exports)
+LIB_PATH = os.environ.get("SQATTN_B200_LIB") or os.path.join(_HERE, "libsqattn_b200.so")
 
 F16, BF16 = 0, 1
 MODE_DENSE_CAUSAL, MODE_RELATIVE_WINDOW, MODE_ABSOLUTE_WINDOW = 0, 1, 2

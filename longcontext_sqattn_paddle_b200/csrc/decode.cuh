@@ -85,6 +85,11 @@ __global__ void __launch_bounds__(160, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ DecodeParams p) {
   using L = DecodeSmem<D>;
+  // Launched with programmatic stream serialisation: this grid may become resident while its predecessor in the
+  // stream drains; nothing the predecessor produced (lengths, q, the status word) is read before this wait, and
+  // the kernel that follows (the merge) may be made resident right away, it waits for this grid in turn.
+  griddep_launch();
+  griddep_wait();
   // after a wait has given up on this device (here or in an earlier launch) the partials of this work item are
   // marked invalid, so that the merge hands NaN to the caller instead of stale scratch
   auto poison_partials = [&](int nthr) {
@@ -331,16 +336,80 @@ struct MergeParams {
 };
 
 // O = sum_i 2^(lse_i - max) O_i / sum_i 2^(lse_i - max);  lse = log2(sum) + max
-// One CTA per output row (b, h).  The partial weights are computed once into shared memory; the partials are
-// then summed by kMergeGroups thread groups in parallel (each takes every kMergeGroups-th partial, four loads
-// in flight per thread) and the groups are combined in a fixed order, so the result does not depend on timing.
+// One CTA (128 * kMergeGroups threads) per output row (b, h).  Thread (group g, column c) takes every
+// kMergeGroups-th partial of column c.  The partial values of a round are loaded into registers BEFORE the
+// weights are known (the loads do not depend on them), so a row costs about one trip to L2 however many
+// partials it has up to kMergeRound; larger counts go in rounds.  The groups are combined in a fixed order, so
+// the result does not depend on timing.
 constexpr int kMergeGroups = 4;
+constexpr int kMergeDepth = 16;                          // partial values in flight per thread
+constexpr int kMergeRound = kMergeGroups * kMergeDepth;  // partials per round
 constexpr int kMergeMaxParts = 2048;
 
+struct MergeScratch {
+  float w[kMergeMaxParts];
+  float red[kMergeGroups][128];
+  float mx[32];
+};
+
+// Merges `count` partials of one row: partial i sits at row (base_row + i * part_stride) of part_o [.., d] /
+// part_lse [..].  Returns this thread's column (tid < d) of the merged, normalised row and the row's LSE (a NaN
+// partial, left by a launch that failed, makes both NaN).  All threads of the CTA must call it.
+__device__ __forceinline__ void merge_row_partials(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                   long long base_row, long long part_stride, int count, int d,
+                                                   MergeScratch& sm, float& out_val, float& out_lse) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int col = tid % 128, grp = tid / 128;
+  float v[kMergeDepth];
+  auto load_round = [&](int base) {
+#pragma unroll
+    for (int u = 0; u < kMergeDepth; ++u) {
+      const int i = base + grp + u * kMergeGroups;
+      v[u] = (i < count && col < d) ? part_o[(base_row + i * part_stride) * d + col] : 0.f;
+    }
+  };
+  load_round(0);
+  float mloc = -INFINITY;
+  for (int i = tid; i < count; i += nthr) mloc = fmaxf(mloc, part_lse[base_row + i * part_stride]);
+  for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+  if ((tid & 31) == 0) sm.mx[tid >> 5] = mloc;
+  __syncthreads();
+  float mmax = -INFINITY;
+  for (int i = 0; i < (nthr + 31) / 32; ++i) mmax = fmaxf(mmax, sm.mx[i]);
+  float den = 0.f, acc = 0.f;
+  for (int base = 0; base < count; base += kMergeMaxParts) {  // more than kMergeMaxParts partials: in batches
+    const int cnt = min(kMergeMaxParts, count - base);
+    __syncthreads();
+    for (int i = tid; i < cnt; i += nthr) {
+      const float lse_i = part_lse[base_row + (base + i) * part_stride];
+      sm.w[i] = (lse_i == -INFINITY) ? 0.f : exp2f(lse_i - mmax);
+    }
+    __syncthreads();
+    for (int i = 0; i < cnt; ++i) den += sm.w[i];  // same order in every thread
+    for (int r0 = 0; r0 < cnt; r0 += kMergeRound) {
+      if (base + r0 > 0) load_round(base + r0);
+#pragma unroll
+      for (int u = 0; u < kMergeDepth; ++u) {
+        const int i = r0 + grp + u * kMergeGroups;
+        if (i < cnt) acc += sm.w[i] * v[u];
+      }
+    }
+  }
+  sm.red[grp][col] = acc;
+  __syncthreads();
+  float tot = 0.f;
+  if (tid < d) {
+#pragma unroll
+    for (int g = 0; g < kMergeGroups; ++g) tot += (g < nthr / 128) ? sm.red[g][tid] : 0.f;
+  }
+  out_val = (den > 0.f) ? tot / den : (den == den ? 0.f : den);
+  out_lse = (den > 0.f) ? log2f(den) + mmax : (den == den ? -INFINITY : den);
+}
+
 __global__ void __launch_bounds__(128 * kMergeGroups) decode_merge_kernel(const __grid_constant__ MergeParams p) {
-  __shared__ float w_s[kMergeMaxParts];
-  __shared__ float red_s[kMergeGroups][128];
-  __shared__ float max_s[32];
+  __shared__ MergeScratch sm;
+  griddep_launch();
+  griddep_wait();  // the partials come from the kernel launched just before
   const long long row = blockIdx.x;  // b*hq + h
   const int b = static_cast<int>(row / p.hq), h = static_cast<int>(row % p.hq);
   int first = 0, count = p.num_parts;
@@ -352,54 +421,16 @@ __global__ void __launch_bounds__(128 * kMergeGroups) decode_merge_kernel(const 
     part_stride = p.hq;
     base_row = static_cast<long long>(first) * p.hq + h;
   }
-  const int tid = threadIdx.x, nthr = blockDim.x;
-  float mloc = -INFINITY;
-  for (int i = tid; i < count; i += nthr) mloc = fmaxf(mloc, p.part_lse[base_row + i * part_stride]);
-  for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
-  if ((tid & 31) == 0) max_s[tid >> 5] = mloc;
-  __syncthreads();
-  float mmax = -INFINITY;
-  for (int i = 0; i < (nthr + 31) / 32; ++i) mmax = fmaxf(mmax, max_s[i]);
-  float den = 0.f;
-  for (int base = 0; base < count; base += kMergeMaxParts) {  // more than kMergeMaxParts partials: in rounds
-    const int cnt = min(kMergeMaxParts, count - base);
-    __syncthreads();
-    for (int i = tid; i < cnt; i += nthr) {
-      const float lse_i = p.part_lse[base_row + (base + i) * part_stride];
-      w_s[i] = (lse_i == -INFINITY) ? 0.f : exp2f(lse_i - mmax);
-    }
-    __syncthreads();
-    for (int i = 0; i < cnt; ++i) den += w_s[i];  // same order in every thread
-    const int col = tid % 128, grp = tid / 128;
-    if (col < p.d) {
-      float acc = (base == 0) ? 0.f : red_s[grp][col];
-      int i = grp;
-      for (; i + 3 * kMergeGroups < cnt; i += 4 * kMergeGroups) {
-        const float v0 = p.part_o[(base_row + (base + i) * part_stride) * p.d + col];
-        const float v1 = p.part_o[(base_row + (base + i + kMergeGroups) * part_stride) * p.d + col];
-        const float v2 = p.part_o[(base_row + (base + i + 2 * kMergeGroups) * part_stride) * p.d + col];
-        const float v3 = p.part_o[(base_row + (base + i + 3 * kMergeGroups) * part_stride) * p.d + col];
-        acc += w_s[i] * v0;
-        acc += w_s[i + kMergeGroups] * v1;
-        acc += w_s[i + 2 * kMergeGroups] * v2;
-        acc += w_s[i + 3 * kMergeGroups] * v3;
-      }
-      for (; i < cnt; i += kMergeGroups) acc += w_s[i] * p.part_o[(base_row + (base + i) * part_stride) * p.d + col];
-      red_s[grp][col] = acc;
-    }
-  }
-  __syncthreads();
+  float val, lse;
+  merge_row_partials(p.part_o, p.part_lse, base_row, part_stride, count, p.d, sm, val, lse);
+  const int tid = threadIdx.x;
   if (tid < p.d) {
-    float acc = 0.f;
-#pragma unroll
-    for (int g = 0; g < kMergeGroups; ++g) acc += (g < nthr / 128) ? red_s[g][tid] : 0.f;
     const int col = tid;
-    const float val = (den > 0.f) ? acc / den : (den == den ? 0.f : den);  // a NaN partial (failed launch) stays NaN
     const long long off = p.contiguous ? row * p.d + col : b * p.o_sb + h * p.o_sh + col;
     if (p.o_f32) reinterpret_cast<float*>(p.o)[off] = val;
     else if (p.o_dtype) reinterpret_cast<uint16_t*>(p.o)[off] = from_f32<true>(val);
     else reinterpret_cast<uint16_t*>(p.o)[off] = from_f32<false>(val);
-    if (col == 0 && p.lse) p.lse[row] = (den > 0.f) ? log2f(den) + mmax : (den == den ? -INFINITY : den);
+    if (col == 0 && p.lse) p.lse[row] = lse;
   }
 }
 

@@ -82,6 +82,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// wait: blocks until the grids this one depends on have completed and their writes are visible (no-op for a normal
+// launch).  launch: once every CTA of this grid has passed it (or exited), the next kernel in the stream, if it was
+// launched with programmatic stream serialisation, may become resident; it still has to `wait` before it reads.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMA
 // 4-D tiled load global -> shared (this CTA), completion counted in bytes on `bar`.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2,

@@ -24,6 +24,19 @@ double sm_scale_log2(int head_dim, int head_dim_og = 0) {
   return 1.0 / sqrt(static_cast<double>(head_dim_og > 0 ? head_dim_og : head_dim)) * 1.44269504;
 }
 
+// Launch with programmatic stream serialisation: the grid may become resident while the kernel before it in the
+// stream drains; the kernel itself waits (griddepcontrol.wait) before it reads anything an earlier kernel produced.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 int elementwise_grid(long long work_items, int block) {
   long long g = (work_items + block - 1) / block;
   const long long cap = 148ll * 16;  // a few waves of the 148 SMs; kernels use grid-stride loops
@@ -218,7 +231,10 @@ struct DecodePlan {
 };
 
 // Length-aware scheduler: every work item covers `chunk` keys of one sequence; chunk is chosen so that all
-// sequences together give about two waves of CTAs (2 CTAs per SM), never less than 256 keys per item.
+// sequences together give about ONE CTA per SM, never less than 256 keys per item.  Measured on B200 (1M keys,
+// 28/4 heads): one CTA per SM keeps 96 KB of loads in flight per SM, which already saturates HBM (6.6 TB/s), and
+// every further split only adds partial rows for the merge to read: 148 / 296 / 596 CTAs gave 162.7 / 165 / 178
+// microseconds per 1 GB layer shard and 4.3 / 7 / 16 microseconds of merge.
 int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
   if (!a) return fail(SQATTN_ERR_INVALID_ARG, "args is null");
   if (a->head_dim != 64 && a->head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", a->head_dim);
@@ -243,7 +259,7 @@ int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
     for (int b = 0; b < a->batch; ++b) maxlen = pl->lens[b] > maxlen ? pl->lens[b] : maxlen;
     chunk = (maxlen + a->num_splits - 1) / a->num_splits;
   } else {
-    const long long target = 148ll * 2 * 2 / a->num_kv_heads + 1;  // items per KV head
+    const long long target = (148ll + a->num_kv_heads - 1) / a->num_kv_heads;  // items per KV head
     chunk = static_cast<int>((total_tiles + target - 1) / target) * kDecTile;
   }
   chunk = (chunk + kDecTile - 1) / kDecTile * kDecTile;
@@ -276,7 +292,7 @@ int fill_peer_params(const sqattn_peer_merge_args* a, PeerMergeParams* p) {
   memset(p, 0, sizeof(*p));
   for (int w = 0; w < a->world; ++w) {
     if (!a->peer_data[w] || !a->peer_flags[w]) return fail(SQATTN_ERR_INVALID_ARG, "peer merge: buffer of rank %d is null", w);
-    p->data[w] = static_cast<float*>(a->peer_data[w]);
+    p->data[w] = static_cast<unsigned long long*>(a->peer_data[w]);
     p->flags[w] = static_cast<uint32_t*>(a->peer_flags[w]);
   }
   p->out = a->out; p->lse = a->lse;
@@ -321,16 +337,14 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   }
   if (pl.total_items > 0) {
     dim3 grid(pl.total_items, a->num_kv_heads);
-    decode_kernel<D, BF16><<<grid, 160, L::kDynBytes, stream>>>(tk, tv, p);
-    SQ_CUDA(cudaGetLastError());
+    SQ_CUDA(launch_overlapped(decode_kernel<D, BF16>, grid, dim3(160), L::kDynBytes, stream, tk, tv, p));
   }
 
   if (a->peer) {
     // the split-KV merge, the exchange with the other GPUs and the merge across GPUs in one kernel
     pm.part_o = p.part_o; pm.part_lse = p.part_lse; pm.split_mode = 1; pm.hq = a->num_q_heads;
     memcpy(pm.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
-    peer_merge_kernel<<<static_cast<unsigned>(pm.rows), 128 * kMergeGroups, 0, stream>>>(pm);
-    SQ_CUDA(cudaGetLastError());
+    SQ_CUDA(launch_overlapped(peer_merge_kernel, dim3(pm.rows), dim3(128 * kMergeGroups), 0, stream, pm));
     return SQATTN_OK;
   }
   MergeParams m;
@@ -343,8 +357,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   } else {
     m.o = a->o.ptr; m.lse = a->lse; m.o_dtype = a->o_dtype; m.o_sb = a->o.stride_b; m.o_sh = a->o.stride_h;
   }
-  decode_merge_kernel<<<static_cast<unsigned>(m.rows), 128 * kMergeGroups, 0, stream>>>(m);
-  SQ_CUDA(cudaGetLastError());
+  SQ_CUDA(launch_overlapped(decode_merge_kernel, dim3(static_cast<unsigned>(m.rows)), dim3(128 * kMergeGroups), 0, stream, m));
   return SQATTN_OK;
 }
 
@@ -373,6 +386,11 @@ int sqattn_debug_schedule(int mode, int n, int sink, int w8, int w4, int p_fp8_m
   const int ns = build_schedule(segs, p, blk, 0);
   for (int i = 0; i < ns; ++i) { out[3 * i] = segs[i].start; out[3 * i + 1] = segs[i].ntiles; out[3 * i + 2] = segs[i].flags; }
   return ns;
+}
+// Debug builds only: where CTA 0 of the cross-GPU merge kernel writes its time stamps ([64][8] int64; null = off)
+int sqattn_debug_set_peer_stamps(long long* stamps) {
+  SQ_CUDA(cudaMemcpyToSymbol(g_peer_stamps, &stamps, sizeof(stamps)));
+  return SQATTN_OK;
 }
 // Debug builds only: same as sqattn_prefill, and CTA 0 additionally writes every S tile it sees
 // ([steps][128 rows][64 keys] fp32) to `dump`.
@@ -831,7 +849,7 @@ int sqattn_silu_mul(const void* x, void* out, int64_t rows, int32_t inter, int32
 
 size_t sqattn_peer_merge_data_bytes(int32_t world, int32_t rows_cap, int32_t head_dim) {
   if (world <= 0 || world > kPeerMaxWorld || rows_cap <= 0 || head_dim <= 0) return 0;
-  return static_cast<size_t>(2) * world * rows_cap * (head_dim + 1) * sizeof(float);
+  return static_cast<size_t>(2) * world * rows_cap * (head_dim + 1) * sizeof(unsigned long long);
 }
 size_t sqattn_peer_merge_flag_bytes(int32_t world, int32_t rows_cap) {
   if (world <= 0 || world > kPeerMaxWorld || rows_cap <= 0) return 0;

@@ -9,10 +9,15 @@ Pinning: the reference has no golden vectors of its own.  The tile kernels
 below are pinned against outputs of the reference's unmodified ``@triton.jit``
 kernels executed by Triton's CPU interpreter (fp16 inputs; the interpreter has
 no bf16); see ``tests/golden/make_golden.py``.  The fake quantisers and the
-adapter glue are Paddle code that cannot be imported where this was written
-(no Paddle): for those parts parity is UNPINNED and rests on reading the
-source.  Two Paddle behaviours are assumed: ``paddle.round`` rounds halves
-away from zero, and ``bf16_tensor / fp32_tensor`` is evaluated in fp32.
+adapter glue (repeat_kv, K centring, quantiser selection, the launchers'
+padding / scaling / window tensors, the output transpose) are Paddle code; they
+are pinned against outputs of that code itself, executed through a ``paddle``
+module that forwards to torch (``tests/golden/paddle_torch_shim.py``): the
+quantisers value for value in fp16 and bf16, ``attention_fn`` end to end.
+What remains an ASSUMPTION, stated in that forwarder, are two Paddle
+behaviours that cannot be observed without Paddle: ``paddle.round`` rounds
+halves away from zero (a switch below selects ties-to-even), and
+``bf16_tensor / fp32_tensor`` is evaluated in fp32.
 """
 from __future__ import annotations
 
@@ -481,13 +486,13 @@ def merge_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor):
 def attention_fn(query, key, value, num_kv_groups: int, bit8_window_sizes, bit4_window_sizes,
                  sink_window_size: int, *, use_relative_distance: bool = True, qk_qtype: str = "int",
                  v_qtype: str = "int", p_fp8_mode: str = "off", round_mode: str = "half_away",
-                 blocks: Optional[Iterable[int]] = None) -> torch.Tensor:
+                 blocks: Optional[Iterable[int]] = None, output_dtype=torch.bfloat16) -> torch.Tensor:
     """mp_triton_wrapper.attention_fn for seq_len > 1: prep -> windowed kernel
     with output_dtype bf16 -> [B, N, Hq*D] (attn_replacer.py:334-365, 423-452)."""
     q8, q4, k8, k4, v8 = prep_qkv(query, key, value, num_kv_groups, qk_qtype, v_qtype, round_mode)
     o = windowed_prefill(q8, k8, q4, k4, v8, bit8_window_sizes, bit4_window_sizes, sink_window_size,
                          mode="relative" if use_relative_distance else "absolute",
-                         tensor_layout="HND", output_dtype=torch.bfloat16, p_fp8_mode=p_fp8_mode,
+                         tensor_layout="HND", output_dtype=output_dtype, p_fp8_mode=p_fp8_mode,
                          blocks=blocks)
     b, h, n, d = o.shape
     return o.transpose(1, 2).contiguous().view(b, n, h * d)

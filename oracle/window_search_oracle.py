@@ -1,7 +1,9 @@
 """CPU oracle for the window calibration (sqattn/window_search.py).
 
-TEST INFRASTRUCTURE ONLY: the shipped package never imports this module.  Parity is UNPINNED by the reference
-(the calibration never receives an attention map as shipped and has no test): this file restates the source.
+TEST INFRASTRUCTURE ONLY: the shipped package never imports this module.  The reference has no test of this
+code; it is pinned against outputs of the reference's own functions (cal_attn_weight, the histogram functions and
+the two threshold searches) executed through a ``paddle`` module that forwards to torch
+(tests/golden/make_golden.py, window_search.npz).
 """
 from __future__ import annotations
 

@@ -86,7 +86,7 @@ def test_a_wait_that_runs_out_is_reported_and_poisons_nothing_silently(pkg):
     rows, d, world = 8, 128, 2
     nd = L.lib.sqattn_peer_merge_data_bytes(world, rows, d) // 4
     nf = L.lib.sqattn_peer_merge_flag_bytes(world, rows) // 4
-    data = [torch.zeros(nd, dtype=torch.float32, device=dev) for _ in range(world)]
+    data = [torch.zeros(nd, dtype=torch.int32, device=dev) for _ in range(world)]
     flags = [torch.zeros(nf, dtype=torch.int32, device=dev) for _ in range(world)]
     epoch = torch.zeros(1, dtype=torch.int32, device=dev)
     po, pl = torch.randn(rows, d, device=dev), torch.randn(rows, device=dev)
@@ -122,14 +122,15 @@ def test_a_wait_that_runs_out_is_reported_and_poisons_nothing_silently(pkg):
     assert (o.float().cpu() - ro.float()).abs().max().item() < 2e-2
     assert torch.isfinite(od.float()).all()
     # and the exchange works once both "ranks" take part: two launches on one GPU must not wait for each other, so
-    # rank 1's flags and data are written by hand before rank 0's kernel runs
-    data = [torch.zeros(nd, dtype=torch.float32, device=dev) for _ in range(world)]
+    # rank 1's words are written by hand before rank 0's kernel runs
+    data = [torch.zeros(nd, dtype=torch.int32, device=dev) for _ in range(world)]
     flags = [torch.zeros(nf, dtype=torch.int32, device=dev) for _ in range(world)]
     epoch.zero_()
     po1, pl1 = torch.randn(rows, d, device=dev), torch.randn(rows, device=dev)
-    slot = data[0].view(2, world, rows, d + 1)           # [parity][source rank][row][D+1]; first call uses parity 1
-    slot[1, 1, :, :d], slot[1, 1, :, d] = po1, pl1
-    flags[0][rows:2 * rows] = 1                          # flag[src = 1][row] = epoch 1
+    # [parity][source rank][row][D+1] words of {fp32 bits, step number}; the first call is step 1 and uses parity 1
+    slot = data[0].view(2, world, rows, d + 1, 2)
+    slot[1, 1, :, :d, 0], slot[1, 1, :, d, 0] = po1.view(torch.int32), pl1.view(torch.int32)
+    slot[1, 1, :, :, 1] = 1
     a = _peer_args(L, world, 0, rows, d, data, flags, epoch, out, po, pl)
     L.check(L.lib.sqattn_decode_peer_merge(C.byref(a), torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
