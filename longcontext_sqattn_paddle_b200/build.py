@@ -39,8 +39,16 @@ def build(force=False, out=OUT, extra=(), verbose=False):
     return out
 
 
+DEBUG_OUT = os.path.join(HERE, "libsqattn_b200_debug.so")
+
+
+def build_debug(force=False, verbose=False):
+    """The same library with the debug exports (tile dumps, time stamps) that some tests and profiling probes read."""
+    return build(force, DEBUG_OUT, ("-DSQATTN_DEBUG_EXPORTS",), verbose)
+
+
 if __name__ == "__main__":
     if "--debug-exports" in sys.argv:
-        build(True, os.path.join(HERE, "libsqattn_b200_debug.so"), ("-DSQATTN_DEBUG_EXPORTS",), True)
+        build_debug(True, True)
     else:
         build("--force" in sys.argv, verbose=True)

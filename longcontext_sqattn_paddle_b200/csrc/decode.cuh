@@ -231,7 +231,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           m_r[r] = m_new;
           mx[r] = m_use;
         }
-        uint32_t pa[4];
+        uint32_t pa[4], pa_lo[4] = {0u, 0u, 0u, 0u};
         float sum[2] = {0.f, 0.f};
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
@@ -242,10 +242,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           if (p.p_fp8) {
             lo16 = p_fp8_round_f16x2(pv[0], pv[1]);
             hi16 = p_fp8_round_f16x2(pv[2], pv[3]);
-            if (BF16) {  // V is bf16: the f16 result is re-rounded to bf16 for the tensor-core product
+            if (BF16) {
+              // V is bf16, so the tensor-core product takes bf16 operands.  The e4m3-rounded P is an f16 value with
+              // up to 11 significant bits: it is split into a bf16 head and a bf16 remainder (exact: at most 3
+              // bits are left), and P V is the sum of two products, so the rounded P reaches the product unchanged
+              // as in the reference's p (f16) * v (fp32), attn_triton_decode.py:229-234.
               const __half2 a = *reinterpret_cast<__half2*>(&lo16), b = *reinterpret_cast<__half2*>(&hi16);
-              lo16 = pack_bf16x2(__low2float(a), __high2float(a));
-              hi16 = pack_bf16x2(__low2float(b), __high2float(b));
+              const float f0 = __low2float(a), f1 = __high2float(a), f2 = __low2float(b), f3 = __high2float(b);
+              lo16 = pack_bf16x2(f0, f1);
+              hi16 = pack_bf16x2(f2, f3);
+              const float h0 = __uint_as_float(lo16 << 16), h1 = __uint_as_float(lo16 & 0xffff0000u);
+              const float h2 = __uint_as_float(hi16 << 16), h3 = __uint_as_float(hi16 & 0xffff0000u);
+              pa_lo[nb * 2] = pack_bf16x2(f0 - h0, f1 - h1);
+              pa_lo[nb * 2 + 1] = pack_bf16x2(f2 - h2, f3 - h3);
             }
           } else {
             lo16 = BF16 ? pack_bf16x2(pv[0], pv[1]) : pack_f16x2(pv[0], pv[1]);
@@ -268,6 +277,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           ldmatrix_x4_trans(v_tile + tile_off(wk + r + (mi & 1) * 8, j * 2 + (mi >> 1)), b0, b1, b2, b3);
           mma_16816<BF16>(o[2 * j], pa, b0, b1);
           mma_16816<BF16>(o[2 * j + 1], pa, b2, b3);
+          if (BF16 && p.p_fp8) {
+            mma_16816<BF16>(o[2 * j], pa_lo, b0, b1);
+            mma_16816<BF16>(o[2 * j + 1], pa_lo, b2, b3);
+          }
         }
       }
       __syncwarp();

@@ -37,6 +37,7 @@ struct PrefillParams {
   long long o_sb, o_sh, o_sn;
   float* lse;
   float* dump;  // debug builds only: S tiles of CTA 0
+  float* dump_p;  // debug builds only: the P tiles CTA 0 hands to the tensor core (f16 values widened to fp32)
   long long* dump_t;  // debug builds only: clock64 stamps of CTA 0, [step][16]
   int batch, hq, hkv, groups, n, kv_len;
   int mode, sink, p_fp8_mode, o_dtype, qk_bf16, same_opset, nblk;
@@ -447,6 +448,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       } else {
 #pragma unroll
         for (int c = 0; c < 32; ++c) pk[c] = 0u;
+      }
+      if (kDump && blockIdx.x == 0 && p.dump_p) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const __half2 h = *reinterpret_cast<const __half2*>(&pk[c]);
+          float* dst = p.dump_p + (static_cast<size_t>(i) * kBlockM + row_in_tile) * 64 + 2 * c;
+          dst[0] = __low2float(h); dst[1] = __high2float(h);
+        }
       }
       tmem_st32(s_tmem, pk);
       // acc *= alpha: O lives in TMEM and is rescaled only when some row of this warp moved its maximum

@@ -115,7 +115,7 @@ int plan_prefill(const sqattn_prefill_args* a, PrefillPlan* pl) {
 
 template <int D>
 int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStream_t stream, float* dump,
-                   long long* dump_t = nullptr) {
+                   long long* dump_t = nullptr, float* dump_p = nullptr) {
   const int B = a->batch, Hq = a->num_q_heads, Hkv = a->num_kv_heads, N = a->qo_len;
   const bool windows = a->mode != SQATTN_MODE_DENSE_CAUSAL;
   const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
@@ -161,7 +161,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   PrefillParams p;
   memset(&p, 0, sizeof(p));
   p.o = a->o.ptr; p.o_sb = a->o.stride_b; p.o_sh = a->o.stride_h; p.o_sn = a->o.stride_n;
-  p.lse = a->lse; p.dump = dump; p.dump_t = dump_t;
+  p.lse = a->lse; p.dump = dump; p.dump_t = dump_t; p.dump_p = dump_p;
   p.batch = B; p.hq = Hq; p.hkv = Hkv; p.groups = Hq / Hkv; p.n = N; p.kv_len = a->kv_len;
   p.mode = a->mode; p.sink = a->sink_size; p.p_fp8_mode = a->p_fp8_mode; p.o_dtype = a->o_dtype;
   p.qk_bf16 = bf16; p.same_opset = alias; p.nblk = (N + kBlockM - 1) / kBlockM;
@@ -182,7 +182,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
 #define SQ_LAUNCH_PREFILL(KS, VS, MINB)                                                                                 \
   do {                                                                                                                   \
     using L = PrefillSmem<D, KS, VS>;                                                                                    \
-    if (dump || dump_t) {                                                                                                \
+    if (dump || dump_t || dump_p) {                                                                                                \
       SQ_CUDA(cudaFuncSetAttribute(prefill_kernel<D, true, KS, VS, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes)); \
       prefill_kernel<D, true, KS, VS, MINB><<<static_cast<unsigned>(grid), 192, L::kDynBytes, stream>>>(tq8, tq4, tk8, tk4, tv, p);    \
     } else {                                                                                                             \
@@ -196,7 +196,8 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   return SQATTN_OK;
 }
 
-int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump, long long* dump_t = nullptr) {
+int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump, long long* dump_t = nullptr,
+                 float* dump_p = nullptr) {
   PrefillPlan pl;
   int rc = plan_prefill(a, &pl);
   if (rc) return rc;
@@ -219,7 +220,8 @@ int prefill_impl(const sqattn_prefill_args* a, cudaStream_t stream, float* dump,
     return fail(SQATTN_ERR_INVALID_ARG, "o needs a 16-byte aligned pointer and strides that are multiples of 8 elements");
   if (pl.total > 0 && (!a->workspace || a->workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(a->workspace) % 1024)))
     return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (1024-byte aligned) required", pl.total);
-  return a->head_dim == 128 ? launch_prefill<128>(a, pl, stream, dump, dump_t) : launch_prefill<64>(a, pl, stream, dump, dump_t);
+  return a->head_dim == 128 ? launch_prefill<128>(a, pl, stream, dump, dump_t, dump_p)
+                            : launch_prefill<64>(a, pl, stream, dump, dump_t, dump_p);
 }
 
 // ---- decode scheduling ---------------------------------------------------------------------------------
@@ -396,6 +398,10 @@ int sqattn_debug_set_peer_stamps(long long* stamps) {
 // ([steps][128 rows][64 keys] fp32) to `dump`.
 int sqattn_debug_prefill_dump(const sqattn_prefill_args* args, float* dump, sqattn_stream_t stream) {
   return prefill_impl(args, reinterpret_cast<cudaStream_t>(stream), dump);
+}
+// ... and the P tiles it hands to the tensor core, same shape
+int sqattn_debug_prefill_dump_sp(const sqattn_prefill_args* args, float* dump_s, float* dump_p, sqattn_stream_t stream) {
+  return prefill_impl(args, reinterpret_cast<cudaStream_t>(stream), dump_s, nullptr, dump_p);
 }
 // ... and clock64 stamps of CTA 0's warps, [steps][16] (see SQ_STAMP in prefill.cuh)
 int sqattn_debug_prefill_timeline(const sqattn_prefill_args* args, float* dump, long long* stamps, sqattn_stream_t stream) {
