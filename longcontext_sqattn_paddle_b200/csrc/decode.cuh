@@ -80,6 +80,11 @@ __device__ __forceinline__ uint32_t tile_off(int key, int chunk) {
   return static_cast<uint32_t>((chunk >> 3) * (kDecTile * 128) + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
 }
 
+#ifdef SQATTN_DEBUG_EXPORTS
+// debug builds only: when the first CTA of a decode launch started and the last one ended (globaltimer)
+__device__ unsigned long long g_dec_first = ~0ull, g_dec_last = 0ull;
+#endif
+
 template <int D, bool BF16>
 __global__ void __launch_bounds__(160, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -90,6 +95,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   // the kernel that follows (the merge) may be made resident right away, it waits for this grid in turn.
   griddep_launch();
   griddep_wait();
+#ifdef SQATTN_DEBUG_EXPORTS
+  if (threadIdx.x == 0) atomicMin(&g_dec_first, globaltimer_ns());
+#endif
   // after a wait has given up on this device (here or in an earlier launch) the partials of this work item are
   // marked invalid, so that the merge hands NaN to the caller instead of stale scratch
   auto poison_partials = [&](int nthr) {
@@ -333,6 +341,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
+#ifdef SQATTN_DEBUG_EXPORTS
+  __syncthreads();
+  if (threadIdx.x == 0) atomicMax(&g_dec_last, globaltimer_ns());
+#endif
 }
 
 struct MergeParams {

@@ -72,6 +72,14 @@ __global__ void __launch_bounds__(128 * kMergeGroups) peer_merge_kernel(const __
   const int dp = p.d + 1;
   const size_t parity_off = static_cast<size_t>(epoch & 1u) * p.world * p.rows_cap * dp;
   SQ_PEER_STAMP(0);
+#ifdef SQATTN_DEBUG_EXPORTS
+  if (g_peer_stamps && blockIdx.x == 0 && tid == 0) {   // span of the decode launch that fed this merge
+    g_peer_stamps[(epoch & 63u) * 8 + 5] = static_cast<long long>(g_dec_first);
+    g_peer_stamps[(epoch & 63u) * 8 + 6] = static_cast<long long>(g_dec_last);
+    g_dec_first = ~0ull;
+    g_dec_last = 0ull;
+  }
+#endif
   if (tid == 0) abort_s = device_failed() ? 1 : 0;   // an earlier failure on this device: no exchange, NaN out
   __syncthreads();
   const bool skip = abort_s != 0;

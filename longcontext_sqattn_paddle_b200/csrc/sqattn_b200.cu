@@ -26,14 +26,27 @@ double sm_scale_log2(int head_dim, int head_dim_og = 0) {
 
 // Launch with programmatic stream serialisation: the grid may become resident while the kernel before it in the
 // stream drains; the kernel itself waits (griddepcontrol.wait) before it reads anything an earlier kernel produced.
+// Which kernels get it is a measured choice (1M-token decode sharded over 2 GPUs, 28 layers per step, graph replay):
+// none 4.806 ms, the merge kernels only 4.800 ms, merge and decode kernels 5.245 ms (a decode grid that becomes
+// resident behind the running one slows it down), so only the merges (class 1) do by default.
+// SQATTN_B200_OVERLAP (read once) overrides: 0 = plain launches, 1 = class 1 only, 2 = all.
+int overlap_level() {
+  static int level = -1;
+  if (level < 0) {
+    const char* e = getenv("SQATTN_B200_OVERLAP");
+    level = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+  }
+  return level;
+}
 template <typename... KArgs, typename... Args>
-cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+cudaError_t launch_overlapped(int klass, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = overlap_level() >= klass ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -339,14 +352,14 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   }
   if (pl.total_items > 0) {
     dim3 grid(pl.total_items, a->num_kv_heads);
-    SQ_CUDA(launch_overlapped(decode_kernel<D, BF16>, grid, dim3(160), L::kDynBytes, stream, tk, tv, p));
+    SQ_CUDA(launch_overlapped(2, decode_kernel<D, BF16>, grid, dim3(160), L::kDynBytes, stream, tk, tv, p));
   }
 
   if (a->peer) {
     // the split-KV merge, the exchange with the other GPUs and the merge across GPUs in one kernel
     pm.part_o = p.part_o; pm.part_lse = p.part_lse; pm.split_mode = 1; pm.hq = a->num_q_heads;
     memcpy(pm.item_prefix, pl.prefix, sizeof(int) * (a->batch + 1));
-    SQ_CUDA(launch_overlapped(peer_merge_kernel, dim3(pm.rows), dim3(128 * kMergeGroups), 0, stream, pm));
+    SQ_CUDA(launch_overlapped(1, peer_merge_kernel, dim3(pm.rows), dim3(128 * kMergeGroups), 0, stream, pm));
     return SQATTN_OK;
   }
   MergeParams m;
@@ -359,7 +372,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   } else {
     m.o = a->o.ptr; m.lse = a->lse; m.o_dtype = a->o_dtype; m.o_sb = a->o.stride_b; m.o_sh = a->o.stride_h;
   }
-  SQ_CUDA(launch_overlapped(decode_merge_kernel, dim3(static_cast<unsigned>(m.rows)), dim3(128 * kMergeGroups), 0, stream, m));
+  SQ_CUDA(launch_overlapped(1, decode_merge_kernel, dim3(static_cast<unsigned>(m.rows)), dim3(128 * kMergeGroups), 0, stream, m));
   return SQATTN_OK;
 }
 
