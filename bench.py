@@ -692,6 +692,54 @@ def run_kernel_only(args):
         qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16)
         fn = lambda: ops.decode(qd, kk, vv, out_dtype=torch.bfloat16)
         work, unit = 2.0 * HKV * n * D * 2 / 1e9, "GB/s"
+    elif args.kernel_only == "kmeans":
+        # one Lloyd iteration (assign + exact re-check + member sums + update) of the clustering of --seq keys per KV head
+        # of the Llama-3-8B geometry into seq/64 centroids: 2*T*K*D flops of assignment work per head
+        from longcontext_sqattn_paddle_b200.cache_hub import kmeans as km
+        from longcontext_sqattn_paddle_b200.cache_hub.retrieval import num_clusters_for
+        g8, kc = 8, num_clusters_for(n)
+        g = torch.Generator(device=dev).manual_seed(3)
+        keys = torch.randn(g8, n, D, device=dev, dtype=torch.bfloat16, generator=g)
+        cent = keys[:, km.init_centroid_indices(n, kc, dev)].contiguous()
+        fn = lambda: km.k_means_train(keys, cent, True)
+        work, unit = 2.0 * g8 * n * kc * D / 1e12, "TFLOP/s"
+    elif args.kernel_only == "window":
+        # the blockwise attention-energy histogram of one layer (28 heads) at --seq tokens: 2*D flops per causal pair
+        from longcontext_sqattn_paddle_b200.sqattn import window_search as ws
+        g = torch.Generator(device=dev).manual_seed(4)
+        qw = torch.randn(HQ, n, D, device=dev, dtype=torch.bfloat16, generator=g)
+        kw = torch.randn(HKV, n, D, device=dev, dtype=torch.bfloat16, generator=g)
+        fn = lambda: ws.attention_histograms(qw, kw, relative=True, num_bins=200, sink_len=SINK)
+        work, unit = 2.0 * 2 * D * HQ * (n * (n + 1) / 2) / 1e12, "TFLOP/s"    # two sweeps (maximum / sum, then weights)
+    elif args.kernel_only == "retrieval":
+        # select + gather + ragged decode for 4 clustered sequences of --seq tokens, 4096-token budget
+        from longcontext_sqattn_paddle_b200.cache_hub import ClusteredKV, RaggedClusteredDecoder
+        caches = [ClusteredKV(torch.randn(8, n, D, device=dev, dtype=torch.bfloat16),
+                              torch.randn(8, n, D, device=dev, dtype=torch.bfloat16), 64, 3) for _ in range(4)]
+        dec = RaggedClusteredDecoder(caches, budget=4096, p_fp8=True)
+        qd = torch.randn(4, 32, 1, D, device=dev, dtype=torch.bfloat16)
+        fn = lambda: dec.step(qd)
+        work, unit = 4.0, "sequences"
+    elif args.kernel_only == "merge":
+        # split-KV decode with both merge kernels: the plain one, and the cross-GPU one run as a world of one rank (its
+        # exchange buffers are ordinary local memory here), so that its instruction stream can be profiled on one GPU
+        import ctypes as C
+        kk = torch.randn(1, HKV, n, D, device=dev, dtype=torch.bfloat16)
+        vv = torch.randn(1, HKV, n, D, device=dev, dtype=torch.bfloat16)
+        qd = torch.randn(1, HQ, 1, D, device=dev, dtype=torch.bfloat16)
+        data = torch.zeros(L.lib.sqattn_peer_merge_data_bytes(1, HQ, D) // 4, dtype=torch.int32, device=dev)
+        flags = torch.zeros(L.lib.sqattn_peer_merge_flag_bytes(1, HQ) // 4, dtype=torch.int32, device=dev)
+        epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        outp = torch.empty(HQ, D, dtype=torch.bfloat16, device=dev)
+        pa = L.PeerMergeArgs()
+        pa.peer_data[0], pa.peer_flags[0] = data.data_ptr(), flags.data_ptr()
+        pa.rank, pa.world, pa.rows, pa.rows_cap, pa.head_dim, pa.epoch = 0, 1, HQ, HQ, D, epoch.data_ptr()
+        pa.out, pa.o_dtype = outp.data_ptr(), L.BF16
+
+        def fn():
+            ops.decode(qd, kk, vv, out_dtype=torch.bfloat16)
+            ops.decode(qd, kk, vv, peer=pa)
+        work, unit = 2 * 2.0 * HKV * n * D * 2 / 1e9, "GB/s"
     elif args.kernel_only == "prep":
         dq, dk, dv = make_inputs(1000, n, device=dev)
         fn = lambda: ops.prep_qkv(dq, dk, dv, skip_bit4=True)
@@ -967,7 +1015,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ttft", action="store_true", help="skip the decoder stand-in's time-to-first-token leg")
-    ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode", "prep"],
+    ap.add_argument("--kernel-only", choices=["prefill", "dense", "decode", "prep", "kmeans", "window", "retrieval", "merge"],
                     help="launch only this kernel --steps times on the bench tensors (for profiler captures)")
     ap.add_argument("--seq", type=int, default=None, help="sequence length for --kernel-only / --workload")
     ap.add_argument("--workload", default="operator", choices=["operator", "ttft", "decode_model", "decode_sp", "decode_hybrid", "retrieval"],

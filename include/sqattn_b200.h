@@ -202,13 +202,16 @@ int sqattn_decode_merge(const float* partial_o, const float* partial_lse, int32_
 
 /* ---- kmeans (cache_hub/kmeans.py) --------------------------------------------------------- */
 
+/* Scratch of sqattn_kmeans_assign and sqattn_kmeans_index_add (flagged-token list, member lists), 256-byte aligned. */
+size_t sqattn_kmeans_workspace_bytes(int32_t groups, int32_t num_tokens, int32_t num_centroids);
 /* _triton_assign_kernel, kmeans.py:7-79: idx[g,t] = argmax_c <data[g,t], centroids[g,c]> (lowest c on
- * ties, exact: near-ties of the fp32 scores are re-evaluated in fp64); sums[g,c,:] (fp64, exact) and
- * counts[g,c] accumulate the members.  sums/counts must be zeroed by the caller.
- * data [G,T,D], centroids [G,K,D] contiguous, dtype f16/bf16, D in {64,128}, K % 32 == 0. */
+ * ties, exact: the fp32 tensor-core scores decide except for near ties, which are re-evaluated in fp64); when sums
+ * is given, sums[g,c,:] (fp64, exact) and counts[g,c] hold the members' sum and number (counts must be zeroed by
+ * the caller; sums is overwritten).  data [G,T,D], centroids [G,K,D] contiguous, dtype f16/bf16, D in {64,128},
+ * K % 32 == 0. */
 int sqattn_kmeans_assign(const void* data, const void* centroids, int32_t dtype, int32_t groups,
                          int32_t num_tokens, int32_t num_centroids, int32_t head_dim, int32_t* idx,
-                         double* sums, int32_t* counts, sqattn_stream_t stream);
+                         double* sums, int32_t* counts, void* workspace, size_t workspace_bytes, sqattn_stream_t stream);
 /* _triton_update_kernel, kmeans.py:82-124: centroid = sums/counts where counts > 0, optional L2 normalise. */
 int sqattn_kmeans_update(void* centroids, int32_t dtype, const double* sums, const int32_t* counts,
                          int32_t groups, int32_t num_centroids, int32_t head_dim, int32_t normalize,
@@ -219,10 +222,10 @@ int sqattn_kmeans_reverse_index(const int32_t* idx, int32_t groups, int32_t num_
                                 int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size,
                                 sqattn_stream_t stream);
 /* triton_index_add, kmeans.py:265-329: value sums per cluster; out [G,K,D] in the value dtype.
- * sums_ws: zeroed fp64 scratch [G,K,D]. */
+ * sums_ws: fp64 scratch [G,K,D]; workspace: sqattn_kmeans_workspace_bytes() bytes. */
 int sqattn_kmeans_index_add(const void* value, int32_t dtype, const int32_t* idx, int32_t groups,
                             int32_t num_tokens, int32_t num_centroids, int32_t head_dim, double* sums_ws,
-                            void* out, sqattn_stream_t stream);
+                            void* out, void* workspace, size_t workspace_bytes, sqattn_stream_t stream);
 /* max over counts[G*K] into *out_max (device int32, zeroed by the caller): data_cnt.max(), kmeans.py:195 */
 int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, sqattn_stream_t stream);
 

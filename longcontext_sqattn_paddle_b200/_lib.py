@@ -100,14 +100,15 @@ SYMBOLS = [
     ("sqattn_decode_static_scratch", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     ("sqattn_decode_merge", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32,
                                       C.c_void_p, C.c_void_p]),
+    ("sqattn_kmeans_workspace_bytes", C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     ("sqattn_kmeans_assign", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
-                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("sqattn_kmeans_update", C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_int32, C.c_void_p]),
     ("sqattn_kmeans_reverse_index", C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                               C.c_void_p, C.c_void_p]),
     ("sqattn_kmeans_index_add", C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
-                                          C.c_void_p, C.c_void_p, C.c_void_p]),
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("sqattn_kmeans_max_count", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     ("sqattn_retrieve_select", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,

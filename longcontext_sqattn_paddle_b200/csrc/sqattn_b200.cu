@@ -8,6 +8,7 @@
 #include "decode.cuh"
 #include "decoder_ops.cuh"
 #include "kmeans.cuh"
+#include "kmeans_tc.cuh"
 #include "peer_exchange.cuh"
 #include "prefill.cuh"
 #include "prep.cuh"
@@ -376,6 +377,66 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   return SQATTN_OK;
 }
 
+// ---- kmeans helpers ----------------------------------------------------------------------------------------
+// scratch of the clustering entry points: [max centroid norm per group | flagged count | flagged list | arrival
+// slot per token | offsets per cluster | member list per group | counts per cluster (index_add only)]
+struct KmWorkspace {
+  float* max_cnorm2; int* flagged_count; int* flagged; int* slot; int* offsets; int* members; int* counts;
+  int flagged_cap;
+  size_t total;
+};
+KmWorkspace km_workspace(void* base, int32_t groups, int32_t num_tokens, int32_t num_centroids) {
+  KmWorkspace w;
+  const size_t gt = static_cast<size_t>(groups) * num_tokens, gk = static_cast<size_t>(groups) * num_centroids;
+  w.flagged_cap = static_cast<int>(gt / 16 > 4096 ? gt / 16 : 4096);
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { uint8_t* r = p ? p + off : nullptr; off += align_up(bytes, 256); return r; };
+  w.max_cnorm2 = reinterpret_cast<float*>(take(groups * sizeof(float)));
+  w.flagged_count = reinterpret_cast<int*>(take(sizeof(int)));
+  w.flagged = reinterpret_cast<int*>(take(static_cast<size_t>(w.flagged_cap) * sizeof(int)));
+  w.slot = reinterpret_cast<int*>(take(gt * sizeof(int)));
+  w.offsets = reinterpret_cast<int*>(take(gk * sizeof(int)));
+  w.members = reinterpret_cast<int*>(take(gt * sizeof(int)));
+  w.counts = reinterpret_cast<int*>(take(gk * sizeof(int)));
+  w.total = off;
+  return w;
+}
+
+// members of every cluster (arrival order) from the assignments, then exact fp64 sums of x over them
+template <int D, bool BF16>
+int km_member_sums(const uint8_t* x, const int32_t* idx, int32_t groups, int32_t num_tokens, int32_t num_centroids,
+                          const KmWorkspace& w, int32_t* counts, double* sums, cudaStream_t stream) {
+  const long long gt = static_cast<long long>(groups) * num_tokens, gk = static_cast<long long>(groups) * num_centroids;
+  kmeans_count_kernel<<<elementwise_grid(gt, 256), 256, 0, stream>>>(idx, counts, w.slot, gt, num_tokens, num_centroids);
+  kmeans_offsets_kernel<<<groups, 1024, 0, stream>>>(counts, w.offsets, num_centroids);
+  kmeans_scatter_kernel<<<elementwise_grid(gt, 256), 256, 0, stream>>>(idx, w.slot, w.offsets, w.members, gt, num_tokens, num_centroids);
+  kmeans_cluster_sum_kernel<D, BF16><<<static_cast<unsigned>((gk * 32 + 255) / 256), 256, 0, stream>>>(
+      x, w.members, w.offsets, counts, sums, gk, num_tokens, num_centroids);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
+template <int D>
+int km_launch_assign(const void* data, const void* centroids, int32_t dtype, int32_t groups, int32_t num_tokens,
+                            int32_t num_centroids, int32_t* idx, const KmWorkspace& w, cudaStream_t stream) {
+  CUtensorMap td, tc;
+  int rc;
+  const int64_t sd = static_cast<int64_t>(num_tokens) * D, sc = static_cast<int64_t>(num_centroids) * D;
+  if ((rc = make_tmap_bhnd(&td, data, dtype, sd * groups, sd, D, 1, groups, num_tokens, D, 128, "kmeans data"))) return rc;
+  if ((rc = make_tmap_bhnd(&tc, centroids, dtype, sc * groups, sc, D, 1, groups, num_centroids, D, kKtCent, "kmeans centroids"))) return rc;
+  KmeansTcParams p;
+  p.data = static_cast<const uint8_t*>(data); p.idx = idx; p.flagged = w.flagged; p.flagged_count = w.flagged_count;
+  p.flagged_cap = w.flagged_cap; p.max_cnorm2 = w.max_cnorm2; p.num_tokens = num_tokens; p.num_centroids = num_centroids;
+  p.bf16 = dtype == SQATTN_BF16;
+  using L = KmeansTcSmem<D>;
+  SQ_CUDA(cudaFuncSetAttribute(kmeans_assign_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  const dim3 grid((num_tokens + kKtTokens - 1) / kKtTokens, groups);
+  kmeans_assign_tc_kernel<D><<<grid, 320, L::kTotal, stream>>>(td, tc, p);
+  SQ_CUDA(cudaGetLastError());
+  return SQATTN_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -598,27 +659,44 @@ static int km_check(int32_t groups, int32_t num_tokens, int32_t num_centroids, i
   return SQATTN_OK;
 }
 
+size_t sqattn_kmeans_workspace_bytes(int32_t groups, int32_t num_tokens, int32_t num_centroids) {
+  if (groups <= 0 || num_tokens <= 0 || num_centroids <= 0) return 0;
+  return km_workspace(nullptr, groups, num_tokens, num_centroids).total;
+}
+
 int sqattn_kmeans_assign(const void* data, const void* centroids, int32_t dtype, int32_t groups, int32_t num_tokens,
                          int32_t num_centroids, int32_t head_dim, int32_t* idx, double* sums, int32_t* counts,
-                         sqattn_stream_t stream_) {
+                         void* workspace, size_t workspace_bytes, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   int rc = km_check(groups, num_tokens, num_centroids, head_dim);
   if (rc) return rc;
   if (!data || !centroids || !idx) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  if (sums && !counts) return fail(SQATTN_ERR_INVALID_ARG, "counts is needed with sums");
+  if (static_cast<long long>(groups) * num_tokens > 0x7fffffffll) return fail(SQATTN_ERR_UNSUPPORTED, "more than 2^31 tokens in all groups");
+  if ((reinterpret_cast<uintptr_t>(data) | reinterpret_cast<uintptr_t>(centroids)) & 15)
+    return fail(SQATTN_ERR_INVALID_ARG, "data and centroids need 16-byte alignment");
+  const size_t need = sqattn_kmeans_workspace_bytes(groups, num_tokens, num_centroids);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required", need);
+  const KmWorkspace w = km_workspace(workspace, groups, num_tokens, num_centroids);
   const bool bf16 = dtype == SQATTN_BF16;
   const uint8_t* d8 = static_cast<const uint8_t*>(data);
   const uint8_t* c8 = static_cast<const uint8_t*>(centroids);
-  dim3 grid((num_tokens + kKmTokens - 1) / kKmTokens, groups);
-  SQ_KM_DISPATCH(kmeans_assign_kernel, <<<grid, 256, 0, stream>>>(d8, c8, idx, num_tokens, num_centroids));
-  const long long warps = static_cast<long long>(groups) * num_tokens;
-  const unsigned rgrid = static_cast<unsigned>((warps * 32 + 255) / 256);
-  SQ_KM_DISPATCH(kmeans_recheck_kernel, <<<rgrid, 256, 0, stream>>>(d8, c8, idx, groups, num_tokens, num_centroids));
-  if (sums) {
-    const long long thr = warps * (head_dim / 8);
-    const unsigned agrid = static_cast<unsigned>((thr + 255) / 256);
-    SQ_KM_DISPATCH(kmeans_accumulate_kernel, <<<agrid, 256, 0, stream>>>(d8, idx, sums, counts, groups, num_tokens, num_centroids));
-  }
+  SQ_CUDA(cudaMemsetAsync(w.flagged_count, 0, sizeof(int), stream));
+  SQ_KM_DISPATCH(kmeans_cnorm_max_kernel, <<<groups, 256, 0, stream>>>(c8, num_centroids, w.max_cnorm2));
+  if ((rc = head_dim == 128 ? km_launch_assign<128>(data, centroids, dtype, groups, num_tokens, num_centroids, idx, w, stream)
+                            : km_launch_assign<64>(data, centroids, dtype, groups, num_tokens, num_centroids, idx, w, stream)))
+    return rc;
+  SQ_KM_DISPATCH(kmeans_recheck_list_kernel, <<<148 * 4, 256, 0, stream>>>(d8, c8, idx, w.flagged, w.flagged_count, w.flagged_cap,
+                                                                        groups, num_tokens, num_centroids));
   SQ_CUDA(cudaGetLastError());
+  if (sums) {
+    if (head_dim == 128) rc = bf16 ? km_member_sums<128, true>(d8, idx, groups, num_tokens, num_centroids, w, counts, sums, stream)
+                                   : km_member_sums<128, false>(d8, idx, groups, num_tokens, num_centroids, w, counts, sums, stream);
+    else rc = bf16 ? km_member_sums<64, true>(d8, idx, groups, num_tokens, num_centroids, w, counts, sums, stream)
+                   : km_member_sums<64, false>(d8, idx, groups, num_tokens, num_centroids, w, counts, sums, stream);
+    if (rc) return rc;
+  }
   return SQATTN_OK;
 }
 
@@ -649,16 +727,24 @@ int sqattn_kmeans_reverse_index(const int32_t* idx, int32_t groups, int32_t num_
 }
 
 int sqattn_kmeans_index_add(const void* value, int32_t dtype, const int32_t* idx, int32_t groups, int32_t num_tokens,
-                            int32_t num_centroids, int32_t head_dim, double* sums_ws, void* out,
-                            sqattn_stream_t stream_) {
+                            int32_t num_centroids, int32_t head_dim, double* sums_ws, void* out, void* workspace,
+                            size_t workspace_bytes, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   int rc = km_check(groups, num_tokens, num_centroids, head_dim);
   if (rc) return rc;
   if (!value || !idx || !sums_ws || !out) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
+  const size_t need = sqattn_kmeans_workspace_bytes(groups, num_tokens, num_centroids);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required", need);
+  const KmWorkspace w = km_workspace(workspace, groups, num_tokens, num_centroids);
   const bool bf16 = dtype == SQATTN_BF16;
   const uint8_t* v8 = static_cast<const uint8_t*>(value);
-  const long long thr = static_cast<long long>(groups) * num_tokens * (head_dim / 8);
-  SQ_KM_DISPATCH(kmeans_accumulate_kernel, <<<static_cast<unsigned>((thr + 255) / 256), 256, 0, stream>>>(v8, idx, sums_ws, nullptr, groups, num_tokens, num_centroids));
+  SQ_CUDA(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(groups) * num_centroids * sizeof(int), stream));
+  if (head_dim == 128) rc = bf16 ? km_member_sums<128, true>(v8, idx, groups, num_tokens, num_centroids, w, w.counts, sums_ws, stream)
+                                 : km_member_sums<128, false>(v8, idx, groups, num_tokens, num_centroids, w, w.counts, sums_ws, stream);
+  else rc = bf16 ? km_member_sums<64, true>(v8, idx, groups, num_tokens, num_centroids, w, w.counts, sums_ws, stream)
+                 : km_member_sums<64, false>(v8, idx, groups, num_tokens, num_centroids, w, w.counts, sums_ws, stream);
+  if (rc) return rc;
   const long long n = static_cast<long long>(groups) * num_centroids * head_dim;
   if (bf16) kmeans_store_sums_kernel<true><<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(sums_ws, static_cast<uint8_t*>(out), n);
   else kmeans_store_sums_kernel<false><<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(sums_ws, static_cast<uint8_t*>(out), n);

@@ -38,7 +38,7 @@ def test_argument_errors_are_status_codes():
     d.head_dim, d.batch, d.num_q_heads, d.num_kv_heads, d.kv_len = 128, 1, 34, 2, 100
     assert L.lib.sqattn_decode(C.byref(d), None) == L.ERR_UNSUPPORTED   # 17 query heads per KV head
     assert L.lib.sqattn_decode_workspace_bytes(C.byref(d)) == 0
-    assert L.lib.sqattn_kmeans_assign(None, None, 0, 1, 10, 33, 128, None, None, None, None) == L.ERR_INVALID_ARG
+    assert L.lib.sqattn_kmeans_assign(None, None, 0, 1, 10, 33, 128, None, None, None, None, 0, None) == L.ERR_INVALID_ARG
     with pytest.raises(ValueError):
         L.check(L.ERR_INVALID_ARG)
 
