@@ -217,10 +217,11 @@ int sqattn_kmeans_update(void* centroids, int32_t dtype, const double* sums, con
                          int32_t groups, int32_t num_centroids, int32_t head_dim, int32_t normalize,
                          sqattn_stream_t stream);
 /* triton_reverse_index, kmeans.py:199-262: member lists sorted by token index.
- * cluster_size [G,K] (output), clusters [G,K,max_cluster_size] (zero-filled by the caller). */
+ * cluster_size [G,K] (output), clusters [G,K,max_cluster_size] (zero-filled by the caller); workspace:
+ * sqattn_kmeans_workspace_bytes() bytes. */
 int sqattn_kmeans_reverse_index(const int32_t* idx, int32_t groups, int32_t num_tokens, int32_t num_centroids,
-                                int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size,
-                                sqattn_stream_t stream);
+                                int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size, void* workspace,
+                                size_t workspace_bytes, sqattn_stream_t stream);
 /* triton_index_add, kmeans.py:265-329: value sums per cluster; out [G,K,D] in the value dtype.
  * sums_ws: fp64 scratch [G,K,D]; workspace: sqattn_kmeans_workspace_bytes() bytes. */
 int sqattn_kmeans_index_add(const void* value, int32_t dtype, const int32_t* idx, int32_t groups,

@@ -106,7 +106,7 @@ SYMBOLS = [
     ("sqattn_kmeans_update", C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_int32, C.c_void_p]),
     ("sqattn_kmeans_reverse_index", C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
-                                              C.c_void_p, C.c_void_p]),
+                                              C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("sqattn_kmeans_index_add", C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("sqattn_kmeans_max_count", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),

@@ -50,8 +50,10 @@ def reverse_index(max_idx: torch.Tensor, num_centroids: int, max_cluster_size: i
     g, t = max_idx.shape
     clusters = torch.zeros(g, num_centroids, max_cluster_size, dtype=torch.int32, device=max_idx.device)
     cluster_size = torch.zeros(g, num_centroids, dtype=torch.int32, device=max_idx.device)
+    need = L.lib.sqattn_kmeans_workspace_bytes(g, t, num_centroids)
+    ws = _workspace(need, max_idx.device)
     L.check(L.lib.sqattn_kmeans_reverse_index(max_idx.data_ptr(), g, t, num_centroids, max_cluster_size,
-                                              clusters.data_ptr(), cluster_size.data_ptr(), _stream()))
+                                              clusters.data_ptr(), cluster_size.data_ptr(), ws.data_ptr(), need, _stream()))
     return clusters, cluster_size
 
 

@@ -10,29 +10,40 @@
 namespace sq {
 
 // centroid = S/C (fp32) where C > 0, optionally / sqrt(sum_d x_d^2) with the sum in fp64 in index order
-// (kmeans.py:116-124); one thread per centroid.
+// (kmeans.py:116-124).  One warp per centroid: a lane takes D/32 consecutive dimensions, and the fp64 sum of squares
+// is passed from lane to lane so that it is added in index order whatever the warp does in parallel.
 template <int D, bool BF16>
-__global__ void kmeans_update_kernel(uint8_t* cent, const double* sums, const int* counts, long long total,
-                                     int normalize) {
-  const long long c = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+__global__ void __launch_bounds__(256)
+kmeans_update_kernel(uint8_t* cent, const double* sums, const int* counts, long long total, int normalize) {
+  constexpr int kPer = D / 32;
+  const long long c = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
   if (c >= total) return;
   const int cnt = counts[c];
   if (cnt <= 0) return;
-  const double* s = sums + c * D;
-  uint16_t* out = reinterpret_cast<uint16_t*>(cent) + c * D;
+  const double* s = sums + c * D + lane * kPer;
+  uint16_t* out = reinterpret_cast<uint16_t*>(cent) + c * D + lane * kPer;
   const float fc = static_cast<float>(cnt);
+  float x[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) x[i] = __fdiv_rn(static_cast<float>(s[i]), fc);
   double nrm = 0.0;
   if (normalize) {
-    for (int d = 0; d < D; ++d) {
-      const double x = static_cast<double>(__fdiv_rn(static_cast<float>(s[d]), fc));
-      nrm += x * x;
+    double run = 0.0;
+    for (int l = 0; l < 32; ++l) {
+      if (lane == l) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) run += static_cast<double>(x[i]) * static_cast<double>(x[i]);
+      }
+      run = __shfl_sync(0xffffffffu, run, l);
     }
-    nrm = sqrt(nrm);
+    nrm = sqrt(run);
   }
-  for (int d = 0; d < D; ++d) {
-    float x = __fdiv_rn(static_cast<float>(s[d]), fc);
-    if (normalize) x = static_cast<float>(static_cast<double>(x) / nrm);
-    out[d] = from_f32<BF16>(x);
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    float v = x[i];
+    if (normalize) v = static_cast<float>(static_cast<double>(v) / nrm);
+    out[i] = from_f32<BF16>(v);
   }
 }
 
@@ -41,42 +52,6 @@ template <bool BF16>
 __global__ void kmeans_store_sums_kernel(const double* sums, uint8_t* out, long long n) {
   const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (i < n) reinterpret_cast<uint16_t*>(out)[i] = from_f32<BF16>(static_cast<float>(sums[i]));
-}
-
-// Member lists in token order.  One CTA per group walks the tokens in order, 1024 at a time; inside a chunk
-// warps take their turn one after the other, and inside a warp tokens of the same cluster are ranked with
-// __match_any_sync, so slot = (members seen so far) + (rank inside the warp).
-__global__ void __launch_bounds__(1024)
-kmeans_reverse_index_kernel(const int* idx, int num_tokens, int num_centroids, int max_cluster_size, int* clusters,
-                            int* cluster_size) {
-  const int g = blockIdx.x;
-  const int* ig = idx + static_cast<long long>(g) * num_tokens;
-  int* cs = cluster_size + static_cast<long long>(g) * num_centroids;
-  int* cl = clusters + static_cast<long long>(g) * num_centroids * max_cluster_size;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = threadIdx.x; c < num_centroids; c += blockDim.x) cs[c] = 0;
-  __syncthreads();
-  for (int base = 0; base < num_tokens; base += 1024) {
-    const int tok = base + threadIdx.x;
-    const bool live = tok < num_tokens;
-    const int c = live ? ig[tok] : -1 - lane;  // dead lanes get distinct keys
-    const unsigned peers = __match_any_sync(0xffffffffu, c);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    const int leader = __ffs(peers) - 1;
-    for (int w = 0; w < 32; ++w) {
-      if (w == warp && live) {
-        int start = 0;
-        if (lane == leader) {
-          start = cs[c];
-          cs[c] = start + __popc(peers);
-        }
-        start = __shfl_sync(peers, start, leader);
-        const int slot = start + rank;
-        if (slot < max_cluster_size) cl[static_cast<long long>(c) * max_cluster_size + slot] = tok;
-      }
-      __syncthreads();
-    }
-  }
 }
 
 __global__ void max_int_kernel(const int* x, long long n, int* out) {

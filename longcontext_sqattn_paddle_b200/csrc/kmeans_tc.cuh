@@ -364,11 +364,22 @@ kmeans_cluster_sum_kernel(const uint8_t* x, const int* members, const int* offse
   constexpr int kRowsPerIter = 32 / kLanesPerRow;
   const int sub = lane / kLanesPerRow, ch = lane % kLanesPerRow;
   double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int m = sub; m < cnt; m += kRowsPerIter) {
-    float f[8];
-    unpack8<BF16>(*reinterpret_cast<const uint4*>(xg + (static_cast<long long>(mem[m]) * D + ch * 8) * 2), f);
+  constexpr int kInFlight = 4;                 // member rows a lane has in flight
+  for (int m0 = sub; m0 < cnt; m0 += kRowsPerIter * kInFlight) {
+    uint4 v[kInFlight];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += static_cast<double>(f[i]);
+    for (int u = 0; u < kInFlight; ++u) {
+      const int m = m0 + u * kRowsPerIter;
+      v[u] = m < cnt ? *reinterpret_cast<const uint4*>(xg + (static_cast<long long>(mem[m]) * D + ch * 8) * 2)
+                     : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      float f[8];
+      unpack8<BF16>(v[u], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += static_cast<double>(f[i]);
+    }
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i)
@@ -377,6 +388,28 @@ kmeans_cluster_sum_kernel(const uint8_t* x, const int* members, const int* offse
     double* dst = sums + w * D + ch * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) dst[i] = acc[i];
+  }
+}
+
+// Member lists in token order from the arrival-order lists: one warp per cluster ranks its members (a member's
+// position is the number of members with a smaller token index) and writes clusters[g, c, :min(n, max_cluster_size)]
+// and cluster_size[g, c] (triton_reverse_index, kmeans.py:199-262, whose own order is the atomic arrival order).
+__global__ void __launch_bounds__(256)
+kmeans_sort_members_kernel(const int* members, const int* offsets, const int* counts, int* clusters, int* cluster_size,
+                           long long total_clusters, int num_tokens, int num_centroids, int max_cluster_size) {
+  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= total_clusters) return;
+  const int g = static_cast<int>(w / num_centroids);
+  const int n = counts[w];
+  const int* mem = members + static_cast<long long>(g) * num_tokens + offsets[w];
+  int* out = clusters + w * max_cluster_size;
+  if (lane == 0) cluster_size[w] = n;
+  for (int i = lane; i < n; i += 32) {
+    const int t = mem[i];
+    int rank = 0;
+    for (int j = 0; j < n; ++j) rank += mem[j] < t ? 1 : 0;     // token indices are distinct
+    if (rank < max_cluster_size) out[rank] = t;
   }
 }
 

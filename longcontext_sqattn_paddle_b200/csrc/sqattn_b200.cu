@@ -708,20 +708,30 @@ int sqattn_kmeans_update(void* centroids, int32_t dtype, const double* sums, con
   if (!centroids || !sums || !counts) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
   const bool bf16 = dtype == SQATTN_BF16;
   const long long total = static_cast<long long>(groups) * num_centroids;
-  const unsigned grid = static_cast<unsigned>((total + 127) / 128);
+  const unsigned grid = static_cast<unsigned>((total * 32 + 255) / 256);
   uint8_t* c8 = static_cast<uint8_t*>(centroids);
-  SQ_KM_DISPATCH(kmeans_update_kernel, <<<grid, 128, 0, stream>>>(c8, sums, counts, total, normalize));
+  SQ_KM_DISPATCH(kmeans_update_kernel, <<<grid, 256, 0, stream>>>(c8, sums, counts, total, normalize));
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
 
 int sqattn_kmeans_reverse_index(const int32_t* idx, int32_t groups, int32_t num_tokens, int32_t num_centroids,
-                                int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size,
-                                sqattn_stream_t stream_) {
+                                int32_t max_cluster_size, int32_t* clusters, int32_t* cluster_size, void* workspace,
+                                size_t workspace_bytes, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!idx || !clusters || !cluster_size) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
   if (groups <= 0 || num_tokens <= 0 || num_centroids <= 0 || max_cluster_size <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
-  kmeans_reverse_index_kernel<<<groups, 1024, 0, stream>>>(idx, num_tokens, num_centroids, max_cluster_size, clusters, cluster_size);
+  const size_t need = sqattn_kmeans_workspace_bytes(groups, num_tokens, num_centroids);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(SQATTN_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required", need);
+  const KmWorkspace w = km_workspace(workspace, groups, num_tokens, num_centroids);
+  const long long gt = static_cast<long long>(groups) * num_tokens, gk = static_cast<long long>(groups) * num_centroids;
+  SQ_CUDA(cudaMemsetAsync(w.counts, 0, static_cast<size_t>(gk) * sizeof(int), stream));
+  kmeans_count_kernel<<<elementwise_grid(gt, 256), 256, 0, stream>>>(idx, w.counts, w.slot, gt, num_tokens, num_centroids);
+  kmeans_offsets_kernel<<<groups, 1024, 0, stream>>>(w.counts, w.offsets, num_centroids);
+  kmeans_scatter_kernel<<<elementwise_grid(gt, 256), 256, 0, stream>>>(idx, w.slot, w.offsets, w.members, gt, num_tokens, num_centroids);
+  kmeans_sort_members_kernel<<<static_cast<unsigned>((gk * 32 + 255) / 256), 256, 0, stream>>>(
+      w.members, w.offsets, w.counts, clusters, cluster_size, gk, num_tokens, num_centroids, max_cluster_size);
   SQ_CUDA(cudaGetLastError());
   return SQATTN_OK;
 }
