@@ -179,11 +179,14 @@ kmeans_assign_tc_kernel(const __grid_constant__ CUtensorMap tm_data, const __gri
     // |k|^2 of this thread's token, from global memory (the tile has just been loaded: an L2 hit)
     float nrm2 = 0.f;
     if (tok < p.num_tokens) {
-      const uint8_t* kr = p.data + (static_cast<long long>(g) * p.num_tokens + tok) * D * 2;
+      const uint4* kr = reinterpret_cast<const uint4*>(p.data + (static_cast<long long>(g) * p.num_tokens + tok) * D * 2);
+      uint4 raw[D / 8];
+#pragma unroll
+      for (int ch = 0; ch < D / 8; ++ch) raw[ch] = kr[ch];          // all loads in flight before the first use
+#pragma unroll
       for (int ch = 0; ch < D / 8; ++ch) {
         float f[8];
-        const uint4 v = *reinterpret_cast<const uint4*>(kr + ch * 16);
-        if (p.bf16) unpack8<true>(v, f); else unpack8<false>(v, f);
+        if (p.bf16) unpack8<true>(raw[ch], f); else unpack8<false>(raw[ch], f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) nrm2 += f[i] * f[i];
       }
@@ -196,13 +199,9 @@ kmeans_assign_tc_kernel(const __grid_constant__ CUtensorMap tm_data, const __gri
       if (!ok) break;
       tc_fence_after();
       const uint32_t s_tmem = tmem + lane_addr + a * kKtCent;
-#pragma unroll 1
-      for (int ch = 0; ch < kKtCent / 32; ++ch) {
-        const int c0 = j * kKtCent + ch * 32;
-        if (c0 >= p.num_centroids) break;        // num_centroids is a multiple of 32: a chunk is whole or absent
-        uint32_t r[32];
-        tmem_ld32(s_tmem + ch * 32, r);
-        tmem_wait_ld();
+      // num_centroids is a multiple of 32: a 32-column chunk is whole or absent
+      const int nch = min(kKtCent / 32, (p.num_centroids - j * kKtCent) / 32);
+      auto scan = [&](const uint32_t (&r)[32], int c0) {
         const float before = best;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -216,6 +215,20 @@ kmeans_assign_tc_kernel(const __grid_constant__ CUtensorMap tm_data, const __gri
           for (int c = 31; c >= 0; --c)
             if (__uint_as_float(r[c]) == best) first = c;
           best_idx = c0 + first;
+        }
+      };
+      // two register buffers: the load of the next chunk is in flight while this one is scanned
+      uint32_t r0[32], r1[32];
+      tmem_ld32(s_tmem, r0);
+#pragma unroll 1
+      for (int ch = 0; ch < nch; ch += 2) {
+        tmem_wait_ld();
+        if (ch + 1 < nch) tmem_ld32(s_tmem + (ch + 1) * 32, r1);
+        scan(r0, j * kKtCent + ch * 32);
+        if (ch + 1 < nch) {
+          tmem_wait_ld();
+          if (ch + 2 < nch) tmem_ld32(s_tmem + (ch + 2) * 32, r0);
+          scan(r1, j * kKtCent + (ch + 1) * 32);
         }
       }
       tc_fence_before();
@@ -246,17 +259,46 @@ kmeans_assign_tc_kernel(const __grid_constant__ CUtensorMap tm_data, const __gri
   }
 }
 
-// Exact re-scoring of the listed tokens: one CTA per token at a time (the CTAs loop over the list), the token in
-// shared memory as fp64, every thread takes centroids tid, tid + 256, ... with 16-byte loads and an index-order
-// fp64 sum, then a CTA-wide argmax with the lowest index winning ties.  When the list overflowed, every token
-// whose idx is still negative is re-scored instead (a sweep over all tokens, the list is ignored).
+// Exact re-scoring of the listed tokens, one CTA per token at a time (the CTAs loop over the list):
+//   1. fp32 scores of ALL centroids of the group into shared memory, a half warp (D = 128) per centroid row with
+//      16-byte loads, so a token costs one coalesced sweep over its group's centroids;
+//   2. the candidates: centroids whose fp32 score lies within the error band of the largest one (the same bound
+//      as in the assignment kernel, which also covers this pass's own rounding);
+//   3. the candidates' exact scores in fp64 (exact products, index-order sum), the largest wins, the lowest index
+//      on ties.  More than kMaxCand candidates (degenerate data, e.g. an all-zero key) take the fp64 path for every
+//      centroid.
+// When the list overflowed, every token whose idx is still negative is re-scored instead (a sweep over all
+// tokens, the list is ignored).
+constexpr int kMaxCand = 64;
+
+template <int D, bool BF16>
+__device__ __forceinline__ double exact_score(const double* kd, const uint8_t* row) {
+  const uint4* x = reinterpret_cast<const uint4*>(row);
+  double s = 0.0;
+#pragma unroll 4
+  for (int ch = 0; ch < D / 8; ++ch) {
+    float f[8];
+    unpack8<BF16>(x[ch], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += kd[ch * 8 + i] * static_cast<double>(f[i]);
+  }
+  return s;
+}
+
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256)
 kmeans_recheck_list_kernel(const uint8_t* data, const uint8_t* cent, int* idx, const int* flagged, const int* flagged_count,
-                           int flagged_cap, int groups, int num_tokens, int num_centroids) {
+                           int flagged_cap, const float* max_cnorm2, int groups, int num_tokens, int num_centroids) {
+  extern __shared__ float score_s[];      // [num_centroids]
   __shared__ double kd[D];
+  __shared__ float red_s[8];
   __shared__ double best_s[8];
   __shared__ int idx_s[8];
+  __shared__ int cand_s[kMaxCand];
+  __shared__ int ncand_s;
+  constexpr int kLanes = D / 8;           // lanes per centroid row
+  constexpr int kRows = 32 / kLanes;      // rows a warp takes at a time
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane / kLanes, ch = lane % kLanes;
   const int count = *flagged_count;
   const bool sweep = count > flagged_cap;
   const long long total = sweep ? static_cast<long long>(groups) * num_tokens : count;
@@ -264,24 +306,72 @@ kmeans_recheck_list_kernel(const uint8_t* data, const uint8_t* cent, int* idx, c
     const long long at = sweep ? e : flagged[e];
     if (sweep && idx[at] >= 0) continue;
     const int g = static_cast<int>(at / num_tokens);
-    const uint16_t* k = reinterpret_cast<const uint16_t*>(data) + at * D;
+    const uint8_t* krow = data + at * D * 2;
     const uint8_t* cg = cent + static_cast<long long>(g) * num_centroids * D * 2;
     __syncthreads();
-    if (threadIdx.x < D) kd[threadIdx.x] = static_cast<double>(to_f32<BF16>(k[threadIdx.x]));
+    float kf[8];
+    unpack8<BF16>(*reinterpret_cast<const uint4*>(krow + ch * 16), kf);
+    if (threadIdx.x < kLanes) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kd[ch * 8 + i] = static_cast<double>(kf[i]);
+    }
+    if (threadIdx.x == 0) ncand_s = 0;
+    float nrm2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) nrm2 += kf[i] * kf[i];
+    for (int o = 1; o < kLanes; o <<= 1) nrm2 += __shfl_xor_sync(0xffffffffu, nrm2, o);
+    // 1. fp32 scores, four rows per half warp in flight
+    float mx = -INFINITY;
+    for (int c0 = warp * kRows + sub; c0 < num_centroids; c0 += 8 * kRows * 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 8 * kRows;
+        v[u] = c < num_centroids ? *reinterpret_cast<const uint4*>(cg + (static_cast<long long>(c) * D + ch * 8) * 2)
+                                 : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 8 * kRows;
+        float f[8], sc = 0.f;
+        unpack8<BF16>(v[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc += kf[i] * f[i];
+        for (int o = 1; o < kLanes; o <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+        if (c < num_centroids) {
+          if (ch == 0) score_s[c] = sc;
+          mx = fmaxf(mx, sc);
+        }
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red_s[warp] = mx;
     __syncthreads();
+    mx = red_s[0];
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_s[w]);
+    // 2. candidates inside the error band
+    const float tol = kKtTol * sqrtf(nrm2) * sqrtf(max_cnorm2[g]);
+    for (int c = threadIdx.x; c < num_centroids; c += 256) {
+      if (score_s[c] >= mx - tol) {
+        const int slot = atomicAdd(&ncand_s, 1);
+        if (slot < kMaxCand) cand_s[slot] = c;
+      }
+    }
+    __syncthreads();
+    const int ncand = ncand_s;
+    // 3. exact scores
     double best = -1.0 / 0.0;
     int bi = 0x7fffffff;
-    for (int c = threadIdx.x; c < num_centroids; c += 256) {
-      const uint4* x = reinterpret_cast<const uint4*>(cg + static_cast<long long>(c) * D * 2);
-      double s = 0.0;
-#pragma unroll 4
-      for (int ch = 0; ch < D / 8; ++ch) {
-        float f[8];
-        unpack8<BF16>(x[ch], f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s += kd[ch * 8 + i] * static_cast<double>(f[i]);
+    if (ncand <= kMaxCand) {
+      if (threadIdx.x < ncand) {
+        bi = cand_s[threadIdx.x];
+        best = exact_score<D, BF16>(kd, cg + static_cast<long long>(bi) * D * 2);
       }
-      if (s > best) { best = s; bi = c; }   // ascending c: the lowest index is kept on ties
+    } else {
+      for (int c = threadIdx.x; c < num_centroids; c += 256) {
+        const double sc = exact_score<D, BF16>(kd, cg + static_cast<long long>(c) * D * 2);
+        if (sc > best) { best = sc; bi = c; }   // ascending c: the lowest index is kept on ties
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -289,7 +379,7 @@ kmeans_recheck_list_kernel(const uint8_t* data, const uint8_t* cent, int* idx, c
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
-    if ((threadIdx.x & 31) == 0) { best_s[threadIdx.x >> 5] = best; idx_s[threadIdx.x >> 5] = bi; }
+    if (lane == 0) { best_s[warp] = best; idx_s[warp] = bi; }
     __syncthreads();
     if (threadIdx.x == 0) {
       for (int w = 1; w < 8; ++w)

@@ -656,6 +656,7 @@ static int km_check(int32_t groups, int32_t num_tokens, int32_t num_centroids, i
   if (head_dim != 64 && head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: only 64 and 128", head_dim);
   if (groups <= 0 || num_tokens <= 0 || num_centroids <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
   if (num_centroids % 32) return fail(SQATTN_ERR_INVALID_ARG, "num_centroids must be a multiple of 32");
+  if (num_centroids > 49152) return fail(SQATTN_ERR_UNSUPPORTED, "at most 49152 centroids per group (their scores are staged in shared memory)");
   return SQATTN_OK;
 }
 
@@ -687,8 +688,18 @@ int sqattn_kmeans_assign(const void* data, const void* centroids, int32_t dtype,
   if ((rc = head_dim == 128 ? km_launch_assign<128>(data, centroids, dtype, groups, num_tokens, num_centroids, idx, w, stream)
                             : km_launch_assign<64>(data, centroids, dtype, groups, num_tokens, num_centroids, idx, w, stream)))
     return rc;
-  SQ_KM_DISPATCH(kmeans_recheck_list_kernel, <<<148 * 4, 256, 0, stream>>>(d8, c8, idx, w.flagged, w.flagged_count, w.flagged_cap,
-                                                                        groups, num_tokens, num_centroids));
+  {
+    const int smem = num_centroids * static_cast<int>(sizeof(float));   // the fp32 scores of one group
+    if (head_dim == 128) {
+      if (bf16) SQ_CUDA(cudaFuncSetAttribute(kmeans_recheck_list_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      else SQ_CUDA(cudaFuncSetAttribute(kmeans_recheck_list_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    } else {
+      if (bf16) SQ_CUDA(cudaFuncSetAttribute(kmeans_recheck_list_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      else SQ_CUDA(cudaFuncSetAttribute(kmeans_recheck_list_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    }
+    SQ_KM_DISPATCH(kmeans_recheck_list_kernel, <<<148 * 4, 256, smem, stream>>>(d8, c8, idx, w.flagged, w.flagged_count, w.flagged_cap,
+                                                                             w.max_cnorm2, groups, num_tokens, num_centroids));
+  }
   SQ_CUDA(cudaGetLastError());
   if (sums) {
     if (head_dim == 128) rc = bf16 ? km_member_sums<128, true>(d8, idx, groups, num_tokens, num_centroids, w, counts, sums, stream)
