@@ -237,11 +237,13 @@ int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, 
  * score (lowest index on ties, empty clusters skipped) until at least `budget` tokens are covered; the tokens of
  * the selected clusters are written to out_idx[g, :out_count[g]] in ascending order (at most `cap`).
  * q [G, heads_per_group, D], centroids [G, K, D], cluster_size [G, K], clusters [G, K, max_cluster_size] as
- * produced by sqattn_kmeans_*; K <= 4096, num_tokens <= 262144. */
+ * produced by sqattn_kmeans_*; K <= 4096, num_tokens <= 262144.  Tokens [tail_start, num_tokens) are the ones
+ * appended since the clusters were last rebuilt: they belong to no cluster yet and are always selected (pass
+ * tail_start = num_tokens when there are none). */
 int sqattn_retrieve_select(const void* q, const void* centroids, int32_t dtype, const int32_t* cluster_size,
                            const int32_t* clusters, int32_t groups_kv, int32_t heads_per_group, int32_t num_clusters,
                            int32_t head_dim, int32_t max_cluster_size, int32_t num_tokens, int32_t budget,
-                           int32_t* out_idx, int32_t* out_count, int32_t cap, sqattn_stream_t stream);
+                           int32_t* out_idx, int32_t* out_count, int32_t cap, int32_t tail_start, sqattn_stream_t stream);
 /* dst[g, j, :] = src[g, idx[g, j], :] for j < count[g] (16-bit rows of head_dim elements; strides in elements) */
 int sqattn_gather_rows(const void* src, int64_t src_group_stride, int64_t src_row_stride, const int32_t* idx,
                        const int32_t* count, int32_t groups, int32_t cap, int32_t head_dim, void* dst,
@@ -262,6 +264,14 @@ typedef struct sqattn_retrieve_item {
   int64_t src_group_stride, src_row_stride;
   void* k_dst;                   /* [G, cap, D] */
   void* v_dst;
+  int32_t tail_start;            /* as in sqattn_retrieve_select */
+  /* block-hybrid caches (cache_hub/cache.py keeps part of the KV on the host): tokens from split_row on are read
+   * from k_src2 / v_src2 [G, tokens - split_row, D] (same row stride), which may be pinned host memory mapped
+   * into the device's address space; NULL: every token is in k_src / v_src */
+  int32_t split_row;
+  const void* k_src2;
+  const void* v_src2;
+  int64_t src2_group_stride;
 } sqattn_retrieve_item;
 int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, int32_t dtype, int32_t groups_kv,
                           int32_t heads_per_group, int32_t head_dim, int32_t budget, int32_t cap, sqattn_stream_t stream);

@@ -78,7 +78,9 @@ class RetrieveItem(C.Structure):
     _fields_ = [("q", C.c_void_p), ("centroids", C.c_void_p), ("cluster_size", C.c_void_p), ("clusters", C.c_void_p),
                 ("num_clusters", C.c_int32), ("max_cluster_size", C.c_int32), ("num_tokens", C.c_int32),
                 ("out_idx", C.c_void_p), ("out_count", C.c_void_p), ("k_src", C.c_void_p), ("v_src", C.c_void_p),
-                ("src_group_stride", C.c_int64), ("src_row_stride", C.c_int64), ("k_dst", C.c_void_p), ("v_dst", C.c_void_p)]
+                ("src_group_stride", C.c_int64), ("src_row_stride", C.c_int64), ("k_dst", C.c_void_p), ("v_dst", C.c_void_p),
+                ("tail_start", C.c_int32), ("split_row", C.c_int32), ("k_src2", C.c_void_p), ("v_src2", C.c_void_p),
+                ("src2_group_stride", C.c_int64)]
 
 
 class PeerMergeArgs(C.Structure):
@@ -112,7 +114,7 @@ SYMBOLS = [
     ("sqattn_kmeans_max_count", C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     ("sqattn_retrieve_select", C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
-                                         C.c_int32, C.c_void_p]),
+                                         C.c_int32, C.c_int32, C.c_void_p]),
     ("sqattn_gather_rows", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                      C.c_int32, C.c_void_p, C.c_void_p]),
     ("sqattn_retrieve_batch", C.c_int, [C.POINTER(RetrieveItem), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

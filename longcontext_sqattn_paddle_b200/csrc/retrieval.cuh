@@ -19,6 +19,8 @@ struct RetrieveParams {
   int* out_idx;             // [G, cap]
   int* out_count;           // [G]
   int groups, num_clusters, d, max_cluster_size, num_tokens, budget, cap;
+  int tail_start;           // tokens [tail_start, num_tokens) are not clustered yet (appended since the last fold) and
+                            // are always selected; tail_start == num_tokens: none
 };
 
 template <bool BF16>
@@ -95,6 +97,9 @@ __device__ __forceinline__ void retrieve_select_body(const RetrieveParams& p, co
     }
   }
   __syncthreads();
+  // tokens appended since the clusters were last rebuilt: always attended
+  for (int tok = p.tail_start + tid; tok < p.num_tokens; tok += blockDim.x) atomicOr(&bitmap[tok >> 5], 1u << (tok & 31));
+  __syncthreads();
   // ordered compaction: each thread owns a contiguous run of bitmap words
   const int per = (words + blockDim.x - 1) / blockDim.x;
   const int w0 = min(words, tid * per), w1 = min(words, w0 + per);
@@ -151,6 +156,11 @@ struct GatherItem {
   const int* idx;       // [G, cap]
   const int* count;     // [G]
   long long src_group_stride, src_row_stride;
+  // block-hybrid caches: rows from split_row on live in a second buffer (pinned host memory, read over PCIe by the
+  // same 16-byte loads), row r of it being token split_row + r; src2 == nullptr: everything is in src
+  const uint8_t* src2;
+  long long src2_group_stride;
+  int split_row;
 };
 struct GatherBatch {
   GatherItem item[2 * kRetMaxBatch];  // keys and values of every sequence
@@ -163,7 +173,10 @@ __global__ void gather_rows_batch_kernel(const __grid_constant__ GatherBatch b, 
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int j = static_cast<int>(i / d8), c = static_cast<int>(i % d8);
     const int tok = it.idx[static_cast<long long>(g) * cap + j];
-    const uint4 v = *reinterpret_cast<const uint4*>(it.src + 2 * (g * it.src_group_stride + tok * it.src_row_stride + c * 8));
+    const uint8_t* row = (it.src2 && tok >= it.split_row)
+                             ? it.src2 + 2 * (g * it.src2_group_stride + static_cast<long long>(tok - it.split_row) * it.src_row_stride)
+                             : it.src + 2 * (g * it.src_group_stride + tok * it.src_row_stride);
+    const uint4 v = *reinterpret_cast<const uint4*>(row + c * 16);
     *reinterpret_cast<uint4*>(it.dst + 2 * ((static_cast<long long>(g) * cap + j) * d + c * 8)) = v;
   }
 }

@@ -785,7 +785,7 @@ int sqattn_kmeans_max_count(const int32_t* counts, int64_t n, int32_t* out_max, 
 int sqattn_retrieve_select(const void* q, const void* centroids, int32_t dtype, const int32_t* cluster_size,
                            const int32_t* clusters, int32_t groups_kv, int32_t heads_per_group, int32_t num_clusters,
                            int32_t head_dim, int32_t max_cluster_size, int32_t num_tokens, int32_t budget,
-                           int32_t* out_idx, int32_t* out_count, int32_t cap, sqattn_stream_t stream_) {
+                           int32_t* out_idx, int32_t* out_count, int32_t cap, int32_t tail_start, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!q || !centroids || !cluster_size || !clusters || !out_idx || !out_count) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
   if (head_dim > 128 || head_dim % 8) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: at most 128, multiple of 8", head_dim);
@@ -797,6 +797,8 @@ int sqattn_retrieve_select(const void* q, const void* centroids, int32_t dtype, 
   p.cluster_size = cluster_size; p.clusters = clusters; p.out_idx = out_idx; p.out_count = out_count;
   p.groups = heads_per_group; p.num_clusters = num_clusters; p.d = head_dim; p.max_cluster_size = max_cluster_size;
   p.num_tokens = num_tokens; p.budget = budget; p.cap = cap;
+  if (tail_start < 0 || tail_start > num_tokens) return fail(SQATTN_ERR_INVALID_ARG, "tail_start %d outside [0, %d]", tail_start, num_tokens);
+  p.tail_start = tail_start;
   const size_t smem = sizeof(double) * num_clusters + sizeof(uint32_t) * ((num_tokens + 31) / 32);
   if (dtype == SQATTN_BF16) {
     SQ_CUDA(cudaFuncSetAttribute(retrieve_select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -849,12 +851,17 @@ int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, 
       p.cluster_size = it.cluster_size; p.clusters = it.clusters; p.out_idx = it.out_idx; p.out_count = it.out_count;
       p.groups = heads_per_group; p.num_clusters = it.num_clusters; p.d = head_dim; p.max_cluster_size = it.max_cluster_size;
       p.num_tokens = it.num_tokens; p.budget = budget; p.cap = cap;
+      if (it.tail_start < 0 || it.tail_start > it.num_tokens || it.split_row < 0)
+        return fail(SQATTN_ERR_INVALID_ARG, "retrieve item %d: tail_start %d / split_row %d out of range", first + i, it.tail_start, it.split_row);
+      p.tail_start = it.tail_start;
       const size_t need = sizeof(double) * it.num_clusters + sizeof(uint32_t) * ((it.num_tokens + 31) / 32);
       smem = need > smem ? need : smem;
       gb.item[2 * i] = GatherItem{static_cast<const uint8_t*>(it.k_src), static_cast<uint8_t*>(it.k_dst), it.out_idx, it.out_count,
-                                  it.src_group_stride, it.src_row_stride};
+                                  it.src_group_stride, it.src_row_stride, static_cast<const uint8_t*>(it.k_src2),
+                                  it.src2_group_stride, it.split_row};
       gb.item[2 * i + 1] = GatherItem{static_cast<const uint8_t*>(it.v_src), static_cast<uint8_t*>(it.v_dst), it.out_idx, it.out_count,
-                                      it.src_group_stride, it.src_row_stride};
+                                      it.src_group_stride, it.src_row_stride, static_cast<const uint8_t*>(it.v_src2),
+                                      it.src2_group_stride, it.split_row};
     }
     const dim3 sgrid(groups_kv, n);
     if (dtype == SQATTN_BF16) {

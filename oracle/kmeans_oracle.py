@@ -133,6 +133,24 @@ def segment_k_means(key, value, num_centroids: int, num_iters: int = 10, num_seg
     return centroids, value_sum, clusters, cluster_size, max_idx
 
 
+def fold_tokens(key, value, assignments, centroids, num_clustered: int):
+    """Growth of a clustered cache (no counterpart in the reference, which clusters once): the tokens from
+    ``num_clustered`` on are assigned to their best centroid by the exact rule of ``assign``, older assignments stay,
+    and centroids, value sums and member lists are recomputed from all assignments with the final iteration's rule
+    (mean of the members, no normalisation, kmeans.py:362-366).
+    key/value [G,T,D], assignments [G,num_clustered] -> (centroids, value_sum, clusters, cluster_size,
+    assignments [G,T])."""
+    g, t, d = key.shape
+    k = centroids.shape[1]
+    new = assign(key[:, num_clustered:], centroids) if t > num_clustered else assignments[:, :0]
+    full = torch.cat([assignments[:, :num_clustered], new], dim=1)
+    s, c = cluster_sums(key, full, k)
+    cent = update(centroids, s, c, False)
+    vsum = index_add(value, full, k)
+    clusters, csize = reverse_index(full, k, int(c.max().item()))
+    return cent, vsum, clusters, csize, full
+
+
 def select_clusters(q_mean: torch.Tensor, centroids: torch.Tensor, cluster_size: torch.Tensor,
                     clusters: torch.Tensor, budget: int):
     """Centroid-scored retrieval (not in the reference; it completes the decode
