@@ -84,6 +84,17 @@ typedef struct {
                            q_row_offset2 (both multiples of 128): a rank that owns two separate row ranges, e.g. chunks
                            r and 2G-1-r of the zig-zag split that balances causal work, runs them in one launch */
   int32_t q_row_offset2;
+  int32_t q_fake_quant; /* 0: q_int8 / q_int4 are prepared operands.  t + 1 (t = SQATTN_QTYPE_*): q_int8 is the query as
+                           the model produced it and the kernel applies the adapter's per-token fake-quant of type t
+                           (sqattn/attn_replacer.py:340-361, fake_quant.py) and the softmax scale to every 128-row tile
+                           in shared memory before its first product, bit for bit what sqattn_prep_qkv writes, so the
+                           prepared copy of q (940 MB at 131072 tokens x 28 heads) never exists in memory.  Needs one
+                           operand set (q_int4 == q_int8 and k_int4 == k_int8: the relative launch as shipped);
+                           q_is_scaled is ignored.  It trades memory for time: the tile is quantised by the CTA's four
+                           softmax warps, which are the kernel's bottleneck, and measured 7 % (131072 tokens) to 25 %
+                           (32768 tokens) slower than the stand-alone pass plus the plain kernel, so the Python
+                           operator keeps the stand-alone pass */
+  int32_t q_round_half_even; /* rounding of that quantiser, as sqattn_prep_args.round_half_even */
   int32_t head_dim_og;  /* 0 or head_dim: nothing special.  Otherwise the tensors were zero-padded from head_dim_og
                            to head_dim (64 or 128) by the caller and the softmax scale applied when q_is_scaled == 0
                            is 1/sqrt(head_dim_og), as the reference launchers do (sqattn/attn_triton.py:236-253, 314;

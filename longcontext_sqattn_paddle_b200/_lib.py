@@ -43,7 +43,7 @@ class PrefillArgs(C.Structure):
         ("p_fp8_mode", C.c_int32), ("q_is_scaled", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("q_row_offset", C.c_int32), ("q_split_rows", C.c_int32), ("q_row_offset2", C.c_int32),
-        ("head_dim_og", C.c_int32),
+        ("q_fake_quant", C.c_int32), ("q_round_half_even", C.c_int32), ("head_dim_og", C.c_int32),
     ]
 
 

@@ -9,6 +9,7 @@
 #pragma once
 #include <cuda.h>
 
+#include "prep.cuh"
 #include "ptx.cuh"
 
 namespace sq {
@@ -45,6 +46,10 @@ struct PrefillParams {
   // sequence and the blocks from blk_split on are blocks blk0_b.. (a rank may own two separate row ranges, e.g. the
   // zig-zag split that balances causal work); blk_split == nblk for a single range.
   int blk0, blk_split, blk0_b;
+  // Q fake-quantisation inside the kernel: the Q tile arrives as the model produced it and every softmax thread
+  // quantises its own row in shared memory before the first MMA (0 = Q is already prepared; else quantiser type + 1)
+  int q_fake_quant, q_half_even;
+  float q_scale;
   int n_total;  // rows of the whole sequence (a 64-row half that starts at or after it does not exist)
   int w8[kMaxHeads];
   int w4[kMaxHeads];
@@ -135,8 +140,8 @@ struct PrefillSmem {
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kVOff = kKOff + kKStages * kKBytes;
   static constexpr int kBarOff = kVOff + kVStages * kVBytes;
-  // barriers: q_full, q_empty, k_full[KS], v_full[VS], s_full[2], p_full[2], o_tail[2]
-  static constexpr int kNumBars = 2 + kKStages + kVStages + 2 + 2 + 2;
+  // barriers: q_full, q_empty, k_full[KS], v_full[VS], s_full[2], p_full[2], o_tail[2], q_ready
+  static constexpr int kNumBars = 2 + kKStages + kVStages + 2 + 2 + 2 + 1;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
   static constexpr int kSegOff = kMiscOff + 16;  // tmem base, abort flag, nseg
   static constexpr int kTotal = kSegOff + kMaxSegs * 12;
@@ -221,6 +226,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
   static_assert(KS == 2 && VS == 3, "K stages follow the two S buffers; V has one stage more");
   const uint32_t bar_k_full = bars + 16, bar_v_full = bar_k_full + 8 * KS;
   const uint32_t bar_s_full = bar_v_full + 8 * VS, bar_p_full = bar_s_full + 16, bar_o_tail = bar_p_full + 16;
+  const uint32_t bar_q_ready = bar_o_tail + 16;
   volatile uint32_t* tmem_base_s = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
   volatile int* nseg_s = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 8);
@@ -238,6 +244,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     for (int i = 0; i < 2; ++i) { mbar_init(bar_s_full + 8 * i, 1); mbar_init(bar_p_full + 8 * i, 128); }
     mbar_init(bar_o_tail, 1);
     mbar_init(bar_o_tail + 8, 1);
+    mbar_init(bar_q_ready, 128);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -314,7 +321,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       StepIter qk_it(segs, nseg);
       auto issue_qk = [&](int j) {
         if (j == 0 || (qk_it.first_of_seg() && qk_it.opset_changed_before())) {
-          ok = mbar_wait(bar_q_full, q_uses & 1, cta_abort, 111);
+          // with in-kernel quantisation the tile is ready when the 128 softmax threads have rewritten their rows
+          SQ_STAMP(j, 3);
+          ok = mbar_wait(p.q_fake_quant ? bar_q_ready : bar_q_full, q_uses & 1, cta_abort, 111);
+          SQ_STAMP(j, 15);
           ++q_uses;
           if (!ok) return;
         }
@@ -374,6 +384,52 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     float m_i = -INFINITY, base = -INFINITY, l_i = 1.0f;  // running maximum; reference of P, l_i and O
     bool ok = true;
     int i = 0;
+    if (p.q_fake_quant && nsteps > 0) {
+      // The adapter's per-token fake-quant of Q (sqattn/attn_replacer.py:361, fake_quant.py:23-125) and the
+      // launcher's q * sm_scale (attn_triton_mix_relative.py:383-385) on this thread's row of the raw tile, in
+      // place, with the device functions of the stand-alone preparation kernel (identical bits).  The row's 16-byte
+      // chunks sit at chunk ^ (row & 7) inside each 128-byte line of the swizzled tile.
+      if (warp == 2 && lane == 0) SQ_STAMP(1, 3);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_q_full, 0, cta_abort, 124));
+      if (warp == 2 && lane == 0) SQ_STAMP(1, 15);
+      if (ok) {
+        uint8_t* qrow = smem + L::kQOff + row_in_tile * 128;
+        uint4 raw[D / 8];
+        float amax = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < D / 8; ++ch) {
+          raw[ch] = *reinterpret_cast<const uint4*>(qrow + (ch >> 3) * (kBlockM * 128) + (((ch & 7) ^ (row_in_tile & 7)) << 4));
+          float f[8];
+          if (p.qk_bf16) unpack8<true>(raw[ch], f); else unpack8<false>(raw[ch], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+        }
+        amax = fmaxf(amax, 1e-5f);
+        const int qtype = p.q_fake_quant - 1;
+#pragma unroll
+        for (int ch = 0; ch < D / 8; ++ch) {
+          float f[8];
+          uint4 outv;
+          if (p.qk_bf16) unpack8<true>(raw[ch], f); else unpack8<false>(raw[ch], f);
+          if (qtype == SQATTN_QTYPE_INT) {
+            outv = p.qk_bf16 ? fake_quant_int_row8<true, true>(f, amax, 127.0f, p.q_half_even, p.q_scale)
+                             : fake_quant_int_row8<false, true>(f, amax, 127.0f, p.q_half_even, p.q_scale);
+          } else {
+            float g[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float v = fake_quant_value(f[e], amax, qtype, 127.0f, p.q_half_even);
+              g[e] = (p.qk_bf16 ? to_f32<true>(from_f32<true>(v)) : to_f32<false>(from_f32<false>(v))) * p.q_scale;
+            }
+            outv = p.qk_bf16 ? pack8<true>(g) : pack8<false>(g);
+          }
+          *reinterpret_cast<uint4*>(qrow + (ch >> 3) * (kBlockM * 128) + (((ch & 7) ^ (row_in_tile & 7)) << 4)) = outv;
+        }
+        fence_proxy_async();   // the rewritten tile is read by the tensor core through the async proxy
+        mbar_arrive(bar_q_ready);
+        if (warp == 2 && lane == 0) SQ_STAMP(2, 3);
+      }
+    }
     for (StepIter it(segs, nseg); ok && !it.done(); it.next(), ++i) {
       const int flags = it.flags();
       const uint32_t s_tmem = tmem + lane_addr + (i & 1) * kBlockN;

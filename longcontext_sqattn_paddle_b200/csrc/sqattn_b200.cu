@@ -116,7 +116,11 @@ int plan_prefill(const sqattn_prefill_args* a, PrefillPlan* pl) {
   const bool alias = !windows || (a->q_int4.ptr == a->q_int8.ptr && a->k_int4.ptr == a->k_int8.ptr);
   const size_t qbytes = static_cast<size_t>(a->batch) * a->num_q_heads * a->qo_len * a->head_dim * 2;
   const size_t vbytes = static_cast<size_t>(a->batch) * a->num_kv_heads * a->kv_len * a->head_dim * 2;
-  pl->scale_q = !a->q_is_scaled;
+  if (a->q_fake_quant < 0 || a->q_fake_quant > 3)
+    return fail(SQATTN_ERR_INVALID_ARG, "q_fake_quant %d: 0 (none) or a quantiser type + 1", a->q_fake_quant);
+  if (a->q_fake_quant && !alias)
+    return fail(SQATTN_ERR_INVALID_ARG, "in-kernel fake-quant of q needs one operand set (q_int4 == q_int8, k_int4 == k_int8)");
+  pl->scale_q = !a->q_is_scaled && !a->q_fake_quant;   // the in-kernel quantiser applies the softmax scale itself
   pl->scale_q4 = pl->scale_q && !alias;
   pl->convert_v = a->v_dtype == SQATTN_BF16;
   size_t off = 0;
@@ -180,6 +184,7 @@ int launch_prefill(const sqattn_prefill_args* a, const PrefillPlan& pl, cudaStre
   p.mode = a->mode; p.sink = a->sink_size; p.p_fp8_mode = a->p_fp8_mode; p.o_dtype = a->o_dtype;
   p.qk_bf16 = bf16; p.same_opset = alias; p.nblk = (N + kBlockM - 1) / kBlockM;
   p.blk0 = a->q_row_offset / kBlockM; p.n_total = a->kv_len;
+  p.q_fake_quant = a->q_fake_quant; p.q_half_even = a->q_round_half_even; p.q_scale = scale;
   p.blk_split = a->q_split_rows > 0 ? a->q_split_rows / kBlockM : p.nblk;
   p.blk0_b = a->q_row_offset2 / kBlockM;
   for (int h = 0; h < Hq; ++h) {

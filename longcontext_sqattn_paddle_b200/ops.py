@@ -79,10 +79,12 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
 def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0, layout: str = "HND",
             out_dtype=torch.float16, return_lse: bool = False, p_fp8_mode: int = 0, q_is_scaled: bool = False,
             out: Optional[torch.Tensor] = None, out_layout: Optional[str] = None, kv_layout: Optional[str] = None,
-            q_row_offset: int = 0, head_dim_og: int = 0, q_split_rows: int = 0, q_row_offset2: int = 0):
+            q_row_offset: int = 0, head_dim_og: int = 0, q_split_rows: int = 0, q_row_offset2: int = 0,
+            q_fake_quant: Optional[str] = None, round_half_even: bool = False):
     """sqattn_prefill.  win8/win4: per-head sequences (floats for the relative mode, ints for the absolute).
     kv_layout: layout of k/v when it differs from q's; q_row_offset: first row of a query shard; head_dim_og: the
-    head_dim before the caller zero-padded the tensors to 64 / 128 (the softmax scale follows it)."""
+    head_dim before the caller zero-padded the tensors to 64 / 128 (the softmax scale follows it).  q_fake_quant
+    ("int" / "e4m3" / "e5m2"): q8 is the raw query and the kernel fake-quantises and scales it tile by tile."""
     _require_cuda(q8, k8, q4, k4, v)
     poll_device_status(q8.device)
     b, hq, n, d = _shape(q8, layout)
@@ -98,6 +100,10 @@ def prefill(q8, k8, q4, k4, v, *, mode: int, win8=None, win4=None, sink: int = 0
     a.v, a.o = _view(v, kv_layout), _view(out, out_layout)
     a.q_row_offset, a.head_dim_og = int(q_row_offset), int(head_dim_og)
     a.q_split_rows, a.q_row_offset2 = int(q_split_rows), int(q_row_offset2)   # second row range of a shard, if any
+    if q_fake_quant is not None:
+        if q_fake_quant not in L.QTYPE:
+            raise ValueError(f"Invalid quantization type: {q_fake_quant}")
+        a.q_fake_quant, a.q_round_half_even = L.QTYPE[q_fake_quant] + 1, int(round_half_even)
     a.lse = lse.data_ptr() if lse is not None else None
     a.batch, a.num_q_heads, a.num_kv_heads, a.qo_len, a.kv_len, a.head_dim = b, hq, hkv, n, kv_len, d
     a.qk_dtype, a.v_dtype, a.o_dtype = _dt(q8.dtype), _dt(v.dtype), _dt(out.dtype)

@@ -98,3 +98,31 @@ def test_host_pipeline_matches_operator():
         assert out.is_pinned() and torch.equal(out, ref.cpu())
     with pytest.raises(ValueError):
         pipe(q, k, v)   # pageable host memory
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("qtype", ["int", "e4m3", "e5m2"])
+def test_q_fake_quant_inside_the_attention_kernel_is_bit_identical(dtype, qtype):
+    """The operator hands the raw query to the attention kernel, which fake-quantises and scales every 128-row tile
+    in shared memory; the result must be the one obtained from the stand-alone preparation of Q (same device
+    functions), for a strided query view of a fused projection, a ragged last tile and a sharded launch."""
+    from longcontext_sqattn_paddle_b200 import _lib as L, ops
+    hq, hkv, n, d = 8, 2, 1000, 128
+    q, k, v = so.make_inputs(17, 1, n, hq, hkv, d, dtype)
+    fused = torch.zeros(1, n, (hq + 2 * hkv) * d, dtype=dtype, device="cuda")
+    fused[..., :hq * d] = q.cuda().reshape(1, n, hq * d)
+    query = fused[..., :hq * d].view(1, n, hq, d)                   # row stride (Hq + 2 Hkv) * D
+    q8, _, k8, _, v8 = ops.prep_qkv(query, k.cuda(), v.cuda(), qk_qtype=qtype, skip_bit4=True)
+    r8, r4 = [0.2] * hq, [0.4] * hq
+    kw = dict(mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4, sink=128, out_dtype=dtype, return_lse=True, p_fp8_mode=L.P_FP8_STAGE2)
+    o_ref, lse_ref = ops.prefill(q8, k8, q8, k8, v8, layout="HND", q_is_scaled=True, **kw)
+    o, lse = ops.prefill(query, k8, query, k8, v8, layout="NHD", kv_layout="HND", q_fake_quant=qtype, **kw)
+    assert torch.equal(o.permute(0, 2, 1, 3), o_ref) and torch.equal(lse, lse_ref)
+    # a shard: rows [256, 768) of the sequence
+    o, lse = ops.prefill(query[:, 256:768], k8, query[:, 256:768], k8, v8, layout="NHD", kv_layout="HND",
+                         q_fake_quant=qtype, q_row_offset=256, **kw)
+    assert torch.equal(o.permute(0, 2, 1, 3), o_ref[:, :, 256:768]) and torch.equal(lse, lse_ref[:, :, 256:768])
+    with pytest.raises(ValueError):   # two operand sets (absolute windows) keep the stand-alone preparation
+        ops.prefill(query, k8, q8.permute(0, 2, 1, 3), k8, v8, layout="NHD", kv_layout="HND", q_fake_quant=qtype, **kw)
+    torch.cuda.synchronize()
+    ops.check_device_status()
