@@ -187,10 +187,11 @@ class CudaBackend:
             return dict(q_row_offset=segs[0][0])
         return dict(q_row_offset=segs[0][0], q_split_rows=segs[0][1] - segs[0][0], q_row_offset2=segs[1][0])
 
-    def windowed_prefill(self, q8, q4, k8, k4, v_full, win8, win4, sink, segs, relative, p_fp8_mode):
+    def windowed_prefill(self, q8, q4, k8, k4, v_full, win8, win4, sink, segs, relative, p_fp8_mode, out=None):
         from . import ops
         b, hq, n, d = q8.shape
-        out = torch.empty(b, n, hq * d, dtype=torch.bfloat16, device=q8.device)
+        if out is None:
+            out = torch.empty(b, n, hq * d, dtype=torch.bfloat16, device=q8.device)
         ops.prefill(q8, k8, q8 if q4 is None else q4, k8 if k4 is None else k4, v_full,
                     mode=L.MODE_RELATIVE_WINDOW if relative else L.MODE_ABSOLUTE_WINDOW, win8=win8, win4=win4, sink=sink,
                     layout="HND", kv_layout="NHD", p_fp8_mode=p_fp8_mode, q_is_scaled=True,
@@ -321,6 +322,65 @@ def _window_reach(win8, win4, relative, total) -> int:
     return max(max(int(x) for x in win8), max(int(x) for x in win4), 0)
 
 
+def _sp_kv_stage(state, backend, key, value, args, win8, win4, sink, total, world, rank, group, layout, exchange):
+    """The K/V half of a sequence-parallel windowed layer: column sums, all-reduce, preparation of this rank's K/V
+    rows into full-length buffers and the exchange of the rows other ranks need.  Returns (k8, k4, v8, segments,
+    outstanding exchange handles); the caller waits on the handles before it launches attention."""
+    relative = bool(args.use_relative_distance)
+    b, ns, hkv, d = key.shape
+    key_ = (total, world, hkv, d, key.dtype, key.device)
+    if state.get("key") != key_:
+        reach = _window_reach(win8, win4, relative, total)
+        lay = _resolve_layout(layout, total, world, reach, sink)
+        # a stage's 64-key tiles may run up to 63 keys past its end, as in the reference loops: the sink rounds up
+        state.update(key=key_, layout=lay, plan=halo_plan(lay, reach, (sink + 63) // 64 * 64),
+                     k8=backend.empty_kv(total, hkv, d, key.dtype, key),
+                     k4=None if relative else backend.empty_kv(total, hkv, d, key.dtype, key),
+                     v8=backend.empty_kv(total, hkv, d, torch.float16, key))
+    lay, k8, k4, v8 = state["layout"], state["k8"], state["k4"], state["v8"]
+    segs = lay.segments(rank)
+    if lay.rows(rank) != ns:
+        raise ValueError(f"rank {rank} holds {ns} tokens, its shard has {lay.rows(rank)}")
+    # 1. global sequence mean of K: all-reduce of the shards' column sums (2 KB) while V is prepared
+    sums = backend.k_column_sums(key)
+    work = dist.all_reduce(sums, group=group, async_op=True) if world > 1 else None
+    base = 0
+    for lo, hi in segs:
+        backend.prep_v(value[:, base:base + hi - lo], args.v_qtype, v8[:, lo:hi])
+        base += hi - lo
+    if work is not None:
+        work.wait()
+    k_mean = (sums / float(total)).contiguous()
+    base = 0
+    for lo, hi in segs:
+        backend.prep_k(key[:, base:base + hi - lo], k_mean, args.qk_qtype, k8[:, lo:hi],
+                       None if k4 is None else k4[:, lo:hi])
+        base += hi - lo
+    # 2. the rows other ranks need travel while Q is prepared
+    works = []
+    if world > 1 and exchange == "halo":
+        p2p = []
+        for src, dst, lo, hi in state["plan"]:
+            for buf in (k8, k4, v8):
+                if buf is None:
+                    continue
+                if src == rank:
+                    p2p.append(dist.P2POp(dist.isend, buf[0, lo:hi], _global_rank(group, dst), group))
+                elif dst == rank:
+                    p2p.append(dist.P2POp(dist.irecv, buf[0, lo:hi], _global_rank(group, src), group))
+        if p2p:
+            works = dist.batch_isend_irecv(p2p)
+    elif world > 1:
+        if lay.kind != "contiguous":
+            raise ValueError("exchange='allgather' needs equal contiguous shards")
+        lo, hi = segs[0]
+        for buf in (k8, k4, v8):
+            if buf is not None:
+                mine = buf[0, lo:hi].clone()
+                works.append(dist.all_gather_into_tensor(buf.view(total, hkv, d), mine, group=group, async_op=True))
+    return k8, k4, v8, segs, works
+
+
 def sp_prefill_wrapper(bit8_window_sizes, bit4_window_sizes, sink_window_size, args, seq_total: Optional[int] = None,
                        group=None, backend=None, p_fp8_mode: int = 0, layout="contiguous", exchange: str = "halo"):
     """Sequence-parallel counterpart of ``mp_triton_wrapper`` (relative or absolute windows): returns
@@ -340,62 +400,13 @@ def sp_prefill_wrapper(bit8_window_sizes, bit4_window_sizes, sink_window_size, a
         relative = bool(args.use_relative_distance)
         world, rank = _group_info(group)
         b, ns, hq, d = query.shape
-        hkv = key.shape[2]
         if b != 1:
             raise ValueError("sequence-parallel prefill takes one sequence (batch 1), like the reference's cache")
         total = seq_total if seq_total is not None else ns * world
         win8 = _per_head(bit8_window_sizes, hq, float if relative else int)
         win4 = _per_head(bit4_window_sizes, hq, float if relative else int)
-        key_ = (total, world, hkv, d, key.dtype, key.device)
-        if state.get("key") != key_:
-            reach = _window_reach(win8, win4, relative, total)
-            lay = _resolve_layout(layout, total, world, reach, sink_window_size)
-            # a stage's 64-key tiles may run up to 63 keys past its end, as in the reference loops: the sink rounds up
-            state.update(key=key_, layout=lay, plan=halo_plan(lay, reach, (sink_window_size + 63) // 64 * 64),
-                         k8=backend.empty_kv(total, hkv, d, key.dtype, key),
-                         k4=None if relative else backend.empty_kv(total, hkv, d, key.dtype, key),
-                         v8=backend.empty_kv(total, hkv, d, torch.float16, key))
-        lay, k8, k4, v8 = state["layout"], state["k8"], state["k4"], state["v8"]
-        segs = lay.segments(rank)
-        if lay.rows(rank) != ns:
-            raise ValueError(f"rank {rank} holds {ns} tokens, its shard has {lay.rows(rank)}")
-        # 1. global sequence mean of K: all-reduce of the shards' column sums (2 KB) while V is prepared
-        sums = backend.k_column_sums(key)
-        work = dist.all_reduce(sums, group=group, async_op=True) if world > 1 else None
-        base = 0
-        for lo, hi in segs:
-            backend.prep_v(value[:, base:base + hi - lo], args.v_qtype, v8[:, lo:hi])
-            base += hi - lo
-        if work is not None:
-            work.wait()
-        k_mean = (sums / float(total)).contiguous()
-        base = 0
-        for lo, hi in segs:
-            backend.prep_k(key[:, base:base + hi - lo], k_mean, args.qk_qtype, k8[:, lo:hi],
-                           None if k4 is None else k4[:, lo:hi])
-            base += hi - lo
-        # 2. the rows other ranks need travel while Q is prepared
-        works = []
-        if world > 1 and exchange == "halo":
-            p2p = []
-            for src, dst, lo, hi in state["plan"]:
-                for buf in (k8, k4, v8):
-                    if buf is None:
-                        continue
-                    if src == rank:
-                        p2p.append(dist.P2POp(dist.isend, buf[0, lo:hi], _global_rank(group, dst), group))
-                    elif dst == rank:
-                        p2p.append(dist.P2POp(dist.irecv, buf[0, lo:hi], _global_rank(group, src), group))
-            if p2p:
-                works = dist.batch_isend_irecv(p2p)
-        elif world > 1:
-            if lay.kind != "contiguous":
-                raise ValueError("exchange='allgather' needs equal contiguous shards")
-            lo, hi = segs[0]
-            for buf in (k8, k4, v8):
-                if buf is not None:
-                    mine = buf[0, lo:hi].clone()
-                    works.append(dist.all_gather_into_tensor(buf.view(total, hkv, d), mine, group=group, async_op=True))
+        k8, k4, v8, segs, works = _sp_kv_stage(state, backend, key, value, args, win8, win4, sink_window_size, total,
+                                               world, rank, group, layout, exchange)
         q8, q4 = backend.prep_q(query, args.qk_qtype, not relative)
         for w in works:
             w.wait()
@@ -403,6 +414,88 @@ def sp_prefill_wrapper(bit8_window_sizes, bit4_window_sizes, sink_window_size, a
 
     attention_fn.state = state
     return attention_fn
+
+
+class SPHostPrefillPipeline:
+    """The sequence-parallel operator for callers whose activations live in PINNED HOST memory (the counterpart of
+    ``sqattn.HostPrefillPipeline`` on N ranks): ``pipe(q_host, k_host, v_host, out_host)`` with this rank's rows
+    q [1,ns,Hq,D], k/v [1,ns,Hkv,D] -> its rows of the output [1,ns,Hq*D].  K and V are uploaded, prepared and
+    exchanged once; Q is uploaded, prepared and attended in chunks of ``chunk_rows`` rows while the previous chunk's
+    output travels back, so the two copy directions, the collectives and the kernels overlap.  Relative windows."""
+
+    def __init__(self, bit8_window_sizes, bit4_window_sizes, sink_window_size, args, seq_total: int, layout="balanced",
+                 chunk_rows: int = 4096, group=None, p_fp8_mode: int = 0, device=None):
+        if chunk_rows % 128:
+            raise ValueError("chunk_rows must be a multiple of 128")
+        if not args.use_relative_distance:
+            raise ValueError("the host pipeline is implemented for relative windows")
+        self.bit8, self.bit4, self.sink, self.args = bit8_window_sizes, bit4_window_sizes, sink_window_size, args
+        self.total, self.layout, self.chunk, self.group, self.fp8 = int(seq_total), layout, int(chunk_rows), group, p_fp8_mode
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.backend, self.state, self._buf = CudaBackend(), {}, None
+
+    def __call__(self, q_host, k_host, v_host, out_host):
+        for t in (q_host, k_host, v_host, out_host):
+            if t.is_cuda or not t.is_pinned():
+                raise ValueError("q, k, v and out must be pinned host tensors")
+        a, be, dev = self.args, self.backend, self.device
+        world, rank = _group_info(self.group)
+        b, ns, hq, d = q_host.shape
+        hkv = k_host.shape[2]
+        win8, win4 = _per_head(self.bit8, hq, float), _per_head(self.bit4, hq, float)
+        if self._buf is None or self._buf["k"].shape != k_host.shape:
+            c = min(self.chunk, ns)
+            self._buf = {"k": torch.empty(k_host.shape, dtype=k_host.dtype, device=dev),
+                         "v": torch.empty(v_host.shape, dtype=v_host.dtype, device=dev),
+                         "q": [torch.empty(1, c, hq, d, dtype=q_host.dtype, device=dev) for _ in range(2)],
+                         "o": [torch.empty(1, c, hq * d, dtype=torch.bfloat16, device=dev) for _ in range(2)]}
+        buf = self._buf
+        cur = torch.cuda.current_stream(dev)
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            buf["k"].copy_(k_host, non_blocking=True)
+            buf["v"].copy_(v_host, non_blocking=True)
+            ev_kv = torch.cuda.Event()
+            ev_kv.record(self.s_in)
+        cur.wait_event(ev_kv)
+        k8, _, v8, segs, works = _sp_kv_stage(self.state, be, buf["k"], buf["v"], a, win8, win4, self.sink, self.total,
+                                              world, rank, self.group, self.layout, "halo")
+        q_free, o_free = [None, None], [None, None]
+        ci, base, waited = 0, 0, False
+        for lo, hi in segs:
+            for r0 in range(0, hi - lo, self.chunk):
+                rows, s = min(self.chunk, hi - lo - r0), ci & 1
+                with torch.cuda.stream(self.s_in):
+                    if q_free[s] is not None:
+                        self.s_in.wait_event(q_free[s])
+                    buf["q"][s][:, :rows].copy_(q_host[:, base + r0:base + r0 + rows], non_blocking=True)
+                    ev_q = torch.cuda.Event()
+                    ev_q.record(self.s_in)
+                cur.wait_event(ev_q)
+                if o_free[s] is not None:
+                    cur.wait_event(o_free[s])
+                q8, _ = be.prep_q(buf["q"][s][:, :rows], a.qk_qtype, False)
+                if not waited:          # the halo rows have to be in place before the first attention launch
+                    for w in works:
+                        w.wait()
+                    waited = True
+                o = be.windowed_prefill(q8, None, k8, None, v8, win8, win4, self.sink, [(lo + r0, lo + r0 + rows)], True,
+                                        self.fp8, out=buf["o"][s][:, :rows])
+                ev_c = torch.cuda.Event()
+                ev_c.record(cur)
+                q_free[s] = ev_c
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(ev_c)
+                    out_host[:, base + r0:base + r0 + rows].copy_(o, non_blocking=True)
+                    ev_o = torch.cuda.Event()
+                    ev_o.record(self.s_out)
+                o_free[s] = ev_o
+                ci += 1
+            base += hi - lo
+        cur.wait_stream(self.s_out)
+        return out_host
 
 
 def sp_dense_wrapper(seq_total: Optional[int] = None, group=None, backend=None, layout="zigzag"):

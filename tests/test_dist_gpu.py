@@ -66,6 +66,19 @@ def _worker(rank, world, port, tmp):
             for _ in range(2):
                 out = fn(_Layer(), _rows(q, segs).cuda(), _rows(k, segs).cuda(), _rows(v, segs).cuda(), None)
             torch.save((segs, out.cpu()), os.path.join(tmp, f"prefill_{name}_{rank}.pt"))
+        # the same operator fed from pinned host buffers, chunked and overlapped: identical rows
+        for layout in ("balanced", "zigzag"):
+            w8, w4, sink = [0.125] * hq, [0.25] * hq, 128
+            reach = sqdist._window_reach(w8, w4, True, n)
+            segs = sqdist._resolve_layout(layout, n, world, reach, sink).segments(rank)
+            ref = sqdist.sp_prefill_wrapper(w8, w4, sink, _Args(), seq_total=n, layout=layout)(
+                _Layer(), _rows(q, segs).cuda(), _rows(k, segs).cuda(), _rows(v, segs).cuda(), None)
+            pipe = sqdist.SPHostPrefillPipeline(w8, w4, sink, _Args(), seq_total=n, layout=layout, chunk_rows=256)
+            hout = torch.empty(ref.shape, dtype=ref.dtype).pin_memory()
+            for _ in range(2):
+                pipe(_rows(q, segs).pin_memory(), _rows(k, segs).pin_memory(), _rows(v, segs).pin_memory(), hout)
+                torch.cuda.synchronize()
+                assert torch.equal(hout, ref.cpu()), layout
         for layout in ("contiguous", "zigzag"):
             fn = sqdist.sp_dense_wrapper(seq_total=n, layout=layout)
             segs = sqdist._resolve_layout(layout, n, world, 0, 0).segments(rank)
