@@ -29,15 +29,15 @@ double sm_scale_log2(int head_dim, int head_dim_og = 0) {
 // stream drains; the kernel itself waits (griddepcontrol.wait) before it reads anything an earlier kernel produced.
 // Which kernels get it is a measured choice (1M-token decode sharded over 2 GPUs, 28 layers per step, graph replay):
 // none 4.806 ms, the merge kernels only 4.800 ms, merge and decode kernels 5.245 ms (a decode grid that becomes
-// resident behind the running one slows it down), so only the merges (class 1) do by default.
-// SQATTN_B200_OVERLAP (read once) overrides: 0 = plain launches, 1 = class 1 only, 2 = all.
-int overlap_level() {
-  static int level = -1;
-  if (level < 0) {
+// resident behind the running one slows it down), so only the merges do by default.
+// SQATTN_B200_OVERLAP (read once) overrides with a bit mask of kernel classes: 1 = merge kernels, 2 = decode kernel.
+int overlap_mask() {
+  static int mask = -1;
+  if (mask < 0) {
     const char* e = getenv("SQATTN_B200_OVERLAP");
-    level = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+    mask = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 1;
   }
-  return level;
+  return mask;
 }
 template <typename... KArgs, typename... Args>
 cudaError_t launch_overlapped(int klass, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -47,7 +47,7 @@ cudaError_t launch_overlapped(int klass, void (*kernel)(KArgs...), dim3 grid, di
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = overlap_level() >= klass ? 1 : 0;
+  cfg.attrs = attr; cfg.numAttrs = (overlap_mask() & klass) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
