@@ -62,8 +62,9 @@ def load_peaks():
     if os.path.exists(p):
         with open(p) as f:
             d = json.load(f)
-        return {"tflops": float(d["bf16_tflops"]), "hbm": float(d["hbm_gbs"]), "src": "measured"}
-    return {"tflops": 1590.0, "hbm": 6650.0, "src": "fallback"}
+        return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "hbm": float(d["hbm_gbs"]), "src": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm": 6650.0, "src": "fallback"}
 
 
 class ClockSampler:
@@ -585,7 +586,10 @@ def run_ours(args):
     rsampler = ClockSampler(ctx.local)
     if rank == 0:
         rsampler.start()
-    ksteps = max(3, args.steps // 2)
+    # Two timings of the same launch.  Burst: three launches after the pause (about 70 ms of work, before the 1 kW power
+    # cap pulls the clocks down), compared with the burst bf16 peak, which was measured the same way (sub-millisecond
+    # GEMMs); sustained: a longer loop, compared with the peak measured in a seconds-long GEMM loop under the cap.
+    ksteps = 3
     ctx.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -595,6 +599,19 @@ def run_ours(args):
     ctx.barrier()
     my_ms = e0.elapsed_time(e1) / ksteps
     rclocks = rsampler.stop() if rank == 0 else None
+    lsteps = max(6, args.steps)
+    for _ in range(lsteps // 2):
+        kern()
+    ssampler = ClockSampler(ctx.local)
+    if rank == 0:
+        ssampler.start()
+    e0.record()
+    for _ in range(lsteps):
+        kern()
+    e1.record()
+    ctx.barrier()
+    sus_ms = ctx.max_over_ranks(e0.elapsed_time(e1) / lsteps)
+    sclocks = ssampler.stop() if rank == 0 else None
     ops.check_device_status()
     my_ach = my_flops / (my_ms * 1e-3) / 1e12
     worst = -ctx.max_over_ranks(-my_ach)          # the slowest GPU's rate
@@ -607,7 +624,11 @@ def run_ours(args):
             "achieved": worst, "clocks": rclocks, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": worst / peaks["tflops"],
             "peak_source": peaks["src"], "ms_per_launch": kms, "seq_len": n_total, "rows_this_rank": ns,
             "algorithmic_bytes": alg_bytes, "traffic": 0.92 * alg_bytes,
-            "traffic_unit": "bytes per launch (ncu capture at 32768 tokens scaled by algorithmic bytes)"}
+            "traffic_unit": "bytes per launch (ncu capture at 32768 tokens scaled by algorithmic bytes)",
+            "timing": f"average of {ksteps} launches after a 1 s pause (burst)",
+            "sustained": {"achieved": my_flops / (sus_ms * 1e-3) / 1e12 if world == 1 else None, "ms_per_launch": sus_ms,
+                          "launches": lsteps, "peak": peaks["tflops_sustained"], "clocks": sclocks,
+                          "frac": (my_flops / (sus_ms * 1e-3) / 1e12 / peaks["tflops_sustained"]) if world == 1 else None}}
     del q8
 
     # ---- the other configurations of the metric, one key each
