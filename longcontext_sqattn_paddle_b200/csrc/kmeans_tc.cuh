@@ -145,17 +145,17 @@ kmeans_assign_tc_kernel(const __grid_constant__ CUtensorMap tm_data, const __gri
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ tcgen05 issuer
-    if (lane == 0) {
+    {  // converged warp, one elected lane issues (operands stay warp-uniform values)
       const uint32_t fmt = p.bf16 ? 1u : 0u;
       const uint32_t idesc = make_idesc(fmt, fmt, 0, 0, 128, kKtCent);
-      bool ok = mbar_wait(bar_a_full, 0, cta_abort, 411);
+      bool ok = mbar_wait_warp(bar_a_full, 0, cta_abort, 411);
       for (int j = 0; ok && j < ntiles; ++j) {
         const int st = j & 1;
-        ok = mbar_wait(bar_b_full + 8 * st, (j >> 1) & 1, cta_abort, 412);
+        ok = mbar_wait_warp(bar_b_full + 8 * st, (j >> 1) & 1, cta_abort, 412);
         if (!ok) break;
         const uint64_t b_desc = smem_desc_sw128(b_s + st * L::kBBytes, 16, 1024);
         for (int a = 0; ok && a < 2; ++a) {
-          if (j >= 1) ok = mbar_wait(bar_s_empty + 8 * a, (j - 1) & 1, cta_abort, 413);
+          if (j >= 1) ok = mbar_wait_warp(bar_s_empty + 8 * a, (j - 1) & 1, cta_abort, 413);
           if (!ok) break;
           tc_fence_after();
           const uint64_t a_desc = smem_desc_sw128(a_s + a * L::kABytes, 16, 1024);
@@ -163,9 +163,9 @@ kmeans_assign_tc_kernel(const __grid_constant__ CUtensorMap tm_data, const __gri
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off_a = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
             const uint32_t off_b = (kk >> 2) * (kKtCent * 128) + (kk & 3) * 32;
-            mma_ss(tmem + a * kKtCent, a_desc + (off_a >> 4), b_desc + (off_b >> 4), idesc, kk > 0);
+            mma_ss_elect(tmem + a * kKtCent, a_desc + (off_a >> 4), b_desc + (off_b >> 4), idesc, kk > 0);
           }
-          tc_commit(bar_s_full + 8 * a);
+          tc_commit_elect(bar_s_full + 8 * a);
         }
       }
     }

@@ -199,7 +199,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
   constexpr uint32_t kOCol = 128;
 #define SQ_STAMP(step, slot)                                                            \
   do {                                                                                 \
-    if (kDump && blockIdx.x == 0 && p.dump_t) p.dump_t[(step) * 16 + (slot)] = clock64(); \
+    if (kDump && blockIdx.x == 0 && p.dump_t && (threadIdx.x & 31) == 0) p.dump_t[(step) * 16 + (slot)] = clock64(); \
   } while (0)
 
   // Heads vary fastest so that the heads of one KV group run together and share K/V tiles in L2;
@@ -302,14 +302,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ tcgen05 issuer
-    // Measured on B200: one tcgen05.mma costs the issuing thread ~107 cycles whatever its size (and an N = 64
-    // instruction occupies the tensor pipe as long as an N = 128 one), one tcgen05.commit ~350 cycles.  With 12
-    // MMAs per step this thread is the critical path of the kernel, so it does nothing else: descriptors are
-    // built once and there is ONE commit per step, behind Q K^T; since one thread's MMAs complete in issue
-    // order that commit also reports P V of two steps earlier, which is all the other warps need to know.
+    // The whole warp runs this loop converged and one elected lane issues each instruction: written as
+    // `if (lane == 0) { ... }` the descriptors and addresses are per-thread values for the compiler and one
+    // tcgen05.mma cost the issuing thread ~107 cycles (a commit ~350), 1200 cycles for the 8 MMAs and the commit
+    // of a Q K^T against ~540 now (clock stamps of a debug build).  An N = 64 instruction occupies the tensor pipe
+    // as long as an N = 128 one.  There is ONE commit per step, behind Q K^T; since one thread's MMAs complete in
+    // issue order that commit also reports P V of two steps earlier, which is all the other warps need to know.
     // Issue order QK(i+1), PV(i): S buffer (i+1)&1 still holds P(i-1), which PV(i-1), issued earlier by this
     // same thread, consumes first (the tensor pipe executes one thread's MMAs in issue order).
-    if (lane == 0) {
+    {
       const uint32_t fmt = p.qk_bf16 ? 1u : 0u;
       const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, kBlockM, kBlockN);
       const uint32_t idesc_pv = make_idesc(0, 0, 0, 1, kBlockM, D);
@@ -323,14 +324,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         if (j == 0 || (qk_it.first_of_seg() && qk_it.opset_changed_before())) {
           // with in-kernel quantisation the tile is ready when the 128 softmax threads have rewritten their rows
           SQ_STAMP(j, 3);
-          ok = mbar_wait(p.q_fake_quant ? bar_q_ready : bar_q_full, q_uses & 1, cta_abort, 111);
+          ok = mbar_wait_warp(p.q_fake_quant ? bar_q_ready : bar_q_full, q_uses & 1, cta_abort, 111);
           SQ_STAMP(j, 15);
           ++q_uses;
           if (!ok) return;
         }
         const int st = j & 1;
         SQ_STAMP(j, 0);
-        ok = mbar_wait(bar_k_full + 8 * st, (j >> 1) & 1, cta_abort, 112);
+        ok = mbar_wait_warp(bar_k_full + 8 * st, (j >> 1) & 1, cta_abort, 112);
         if (!ok) return;
         tc_fence_after();
         const uint32_t d_tmem = tmem + st * kBlockN;
@@ -341,22 +342,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
           const uint32_t off_q = (kk >> 2) * kHalfQ + (kk & 3) * 32;
           const uint32_t off_k = (kk >> 2) * kHalfK + (kk & 3) * 32;
           // descriptors differ from the precomputed bases only in the start-address field (units of 16 bytes)
-          mma_ss(d_tmem, q_desc + (off_q >> 4), k_desc + (off_k >> 4), idesc_qk, kk > 0);
+          mma_ss_elect(d_tmem, q_desc + (off_q >> 4), k_desc + (off_k >> 4), idesc_qk, kk > 0);
         }
-        tc_commit(bar_s_full + 8 * st);
+        tc_commit_elect(bar_s_full + 8 * st);
         SQ_STAMP(j, 1);
-        if (qk_it.last_of_seg() && qk_it.opset_changes_after()) tc_commit(bar_q_empty);
+        if (qk_it.last_of_seg() && qk_it.opset_changes_after()) tc_commit_elect(bar_q_empty);
         qk_it.next();
       };
       if (nsteps > 0) issue_qk(0);
       for (int i = 0; ok && i < nsteps; ++i) {
         if (i + 1 < nsteps) { issue_qk(i + 1); if (!ok) break; }
         const int st = i & 1;
-        ok = mbar_wait(bar_p_full + 8 * st, (i >> 1) & 1, cta_abort, 113);
+        ok = mbar_wait_warp(bar_p_full + 8 * st, (i >> 1) & 1, cta_abort, 113);
         if (!ok) break;
         SQ_STAMP(i, 2);
         const int vst = i % 3;
-        ok = mbar_wait(bar_v_full + 8 * vst, (i / 3) & 1, cta_abort, 114);
+        ok = mbar_wait_warp(bar_v_full + 8 * vst, (i / 3) & 1, cta_abort, 114);
         if (!ok) break;
         tc_fence_after();
         const uint32_t p_tmem = tmem + st * kBlockN;
@@ -365,11 +366,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // V tile: [64 keys][64 d] 128-byte rows per d-half; MN-major B operand: 64-d chunks 8 KB apart
           // (leading offset), 8-key groups 1 KB apart (stride offset); 16 keys per MMA = 2 KB.
-          mma_ts(tmem + kOCol, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc_pv, (i > 0 || kk > 0));
+          mma_ts_elect(tmem + kOCol, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc_pv, (i > 0 || kk > 0));
         }
         // Completion of P V(i) is reported by the commit behind Q K^T(i+2); only the last two steps, which no
         // later Q K^T follows, get a commit of their own (slot 0: last step, slot 1: the one before).
-        if (i + 2 >= nsteps) tc_commit(bar_o_tail + 8 * (nsteps - 1 - i));
+        if (i + 2 >= nsteps) tc_commit_elect(bar_o_tail + 8 * (nsteps - 1 - i));
         SQ_STAMP(i, 4);
       }
     }
