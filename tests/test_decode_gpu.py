@@ -97,11 +97,15 @@ def test_decode_partial_and_merge(ops):
     assert (merged.float().cpu() - ro).abs().max().item() < 1e-2
 
 
+@pytest.mark.parametrize("name", ["decode", "decode_large"])
 @pytest.mark.parametrize("fp8", [False, True])
-def test_decode_reference_golden(golden_dir, fp8):
-    """attn_unified (K centred per call like the reference) against the reference kernel's own output."""
+def test_decode_reference_golden(golden_dir, name, fp8):
+    """attn_unified (K centred per call like the reference) against the reference kernel's own output.
+    Bound 8e-3 on O, 3e-2 on LSE (the reference sums q*k products in 16 bits).  Observed on a B200 (max|dO| /
+    max|dLSE|): decode (600 keys) 5.2e-4 / 2.5e-4, with P through e4m3 6.8e-3 / 2.5e-4; decode_large (4096 keys,
+    64 tiles, 7:1 heads) 3.1e-4 / 1.9e-4, with P through e4m3 3.1e-3 / 1.9e-4."""
     from longcontext_sqattn_paddle_b200.sqattn import attn_unified
-    z = np.load(os.path.join(golden_dir, "decode.npz"))
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
     q, k, v = (torch.from_numpy(z[n]).cuda() for n in ("q", "k", "v"))
     o, lse = attn_unified(q, k, v, "HND", torch.float16, True, fp8)
     go, gl = torch.from_numpy(z["o_fp8" if fp8 else "o"]), torch.from_numpy(z["lse_fp8" if fp8 else "lse"])

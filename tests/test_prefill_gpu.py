@@ -128,13 +128,17 @@ def test_absolute_windows(sq, dtype, n, d, sink, w8, w4, fp8):
     _cmp(o, lse, ro, rlse)
 
 
-@pytest.mark.parametrize("name", ["relative", "absolute", "dense"])
+@pytest.mark.parametrize("name", ["relative", "relative_large", "absolute", "dense"])
 @pytest.mark.parametrize("fp8", [False, True])
 def test_against_reference_golden(sq, golden_dir, name, fp8):
-    """The CUDA path against the vectors produced by the reference's own Triton kernels."""
+    """The CUDA path against the vectors produced by the reference's own Triton kernels (fp16 outputs).
+    Bound 6e-3 on O, 2e-3 on LSE.  Observed on a B200 (max|dO| / max|dLSE|, P in f16 | P through e4m3):
+    relative 9.8e-4 / 7.6e-6 | 4.9e-4 / 5.7e-6; relative_large (D 128, 1024 tokens, sink 256, 7:1 heads, per-head
+    ratios) 9.8e-4 / 6.7e-6 | 1.1e-3 / 6.7e-6; absolute 4.9e-4 / 1.9e-6 | 2.4e-4 / 9.5e-7; dense 4.9e-4 / 1.4e-6 |
+    2.4e-3 / 1.4e-6: one or two fp16 ulps of O."""
     z = np.load(os.path.join(golden_dir, name + ".npz"))
     g = {k: torch.from_numpy(z[k]) for k in z.files if z[k].shape != ()}
-    if name == "relative":
+    if name.startswith("relative"):
         o, lse = sq.attn_hierarchical_relative_window(g["q"].cuda(), g["k"].cuda(), g["q"].cuda(), g["k"].cuda(),
                                                       g["v"].cuda(), g["r8"], g["r4"], int(z["sink"]), "HND",
                                                       torch.float16, True, fp8)
@@ -145,6 +149,38 @@ def test_against_reference_golden(sq, golden_dir, name, fp8):
     else:
         o, lse = sq.attn_causal(g["q"].cuda(), g["k"].cuda(), g["v"].cuda(), "HND", torch.float16, True, fp8)
     _cmp(o, lse, g["o_fp8" if fp8 else "o"], g["lse_fp8" if fp8 else "lse"], tol_o=6e-3)
+
+
+@pytest.mark.parametrize("case", ["rel_int", "rel_e4m3", "abs_int", "abs_e5m2"])
+def test_operator_against_reference_adapter_golden(golden_dir, case):
+    """mp_triton_wrapper(...) of this library (fake-quant preparation + kernel, bf16 output) against the output of the
+    reference's own adapter + launcher + kernels on the same fp16 inputs (fixture rounded to fp16).  Bound 2e-2;
+    observed max|dO| 7.8e-3 (rel_int, abs_int, abs_e5m2) and 3.9e-3 (rel_e4m3), i.e. one bf16 ulp of an output near
+    1, with fewer than 4e-4 of the elements above 4e-3."""
+    from longcontext_sqattn_paddle_b200.sqattn import mp_triton_wrapper
+    z = np.load(os.path.join(golden_dir, "adapter.npz"))
+    rel = case.startswith("rel")
+
+    class Args:
+        qk_qtype = {"rel_int": "int", "rel_e4m3": "e4m3", "abs_int": "int", "abs_e5m2": "e5m2"}[case]
+        v_qtype = "e4m3" if case == "rel_e4m3" else "int"
+        use_relative_distance = rel
+
+    class Layer:
+        num_key_value_groups = 2
+
+    if rel:
+        w8, w4 = [float(x) for x in z[f"w8_{case}"]], [float(x) for x in z[f"w4_{case}"]]
+    else:
+        w8, w4 = int(z[f"w8_{case}"]), int(z[f"w4_{case}"])
+    fn = mp_triton_wrapper(1, w8, w4, int(z["sink"]), Args())
+    q, k, v = (torch.from_numpy(z[n]).cuda() for n in ("q", "k", "v"))
+    out = fn(Layer(), q, k, v, None).float().cpu()
+    ref = torch.from_numpy(z[f"o_{case}"]).float()
+    assert out.shape == ref.shape
+    err = (out - ref).abs()
+    assert err.max().item() < TOL_O, err.max().item()
+    assert (err > 4e-3).float().mean().item() < 2e-3
 
 
 def test_config2_blocks_32k(sq):
