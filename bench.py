@@ -67,6 +67,19 @@ def load_peaks():
     return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm": 6650.0, "src": "fallback"}
 
 
+def captured_traffic_ratio():
+    """DRAM bytes of the attention kernel's ncu capture over its algorithmic Q+K+V+O bytes, read from the committed
+    summary of that capture (the table row `DRAM traffic ... | X MB = R x the algorithmic bytes`)."""
+    import re
+    path = os.path.join(ROOT, "profiles", "prefill_kernel_relative_window_32k.md")
+    try:
+        with open(path) as f:
+            m = re.search(r"DRAM traffic[^|]*\|\s*([0-9.]+) MB = ([0-9.]+) x the algorithmic bytes", f.read())
+        return float(m.group(2)), "profiles/prefill_kernel_relative_window_32k.md"
+    except Exception:
+        return None, None
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -619,14 +632,16 @@ def run_ours(args):
     worst = -ctx.max_over_ranks(-my_ach)          # the slowest GPU's rate
     kms = ctx.max_over_ranks(my_ms)
     # DRAM traffic of one launch: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised in
-    # profiles/ for this kernel (taken at 32768 tokens, where it is 0.92 of the algorithmic Q+K+V+O bytes), scaled to
+    # profiles/ for this kernel (taken at 32768 tokens; its ratio to the algorithmic Q+K+V+O bytes is read from that file), scaled to
     # this launch by the algorithmic bytes, which grow with the rows like the traffic does
     alg_bytes = 2.0 * D * (2 * HQ * ns + 2 * HKV * min(n_total, ns + w + SINK))
+    traffic_ratio, traffic_src = captured_traffic_ratio()
     roof = {"bound": "tensor", "kernel": "prefill_kernel<128> (relative windows)" + (", per GPU, slowest rank" if world > 1 else ""),
             "achieved": worst, "clocks": rclocks, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": worst / peaks["tflops"],
             "peak_source": peaks["src"], "ms_per_launch": kms, "seq_len": n_total, "rows_this_rank": ns,
-            "algorithmic_bytes": alg_bytes, "traffic": 0.92 * alg_bytes,
+            "algorithmic_bytes": alg_bytes, "traffic": (traffic_ratio * alg_bytes) if traffic_ratio else None,
             "traffic_unit": "bytes per launch (ncu capture at 32768 tokens scaled by algorithmic bytes)",
+            "traffic_source": traffic_src,
             "timing": f"average of {ksteps} launches after a 1 s pause (burst)",
             "sustained": {"achieved": sus_ach, "ms_per_launch": sus_ms, "launches": lsteps, "peak": peaks["tflops_sustained"],
                           "clocks": sclocks, "frac": sus_ach / peaks["tflops_sustained"]}}

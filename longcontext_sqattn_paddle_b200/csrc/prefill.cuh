@@ -353,12 +353,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant_
       for (int i = 0; ok && i < nsteps; ++i) {
         if (i + 1 < nsteps) { issue_qk(i + 1); if (!ok) break; }
         const int st = i & 1;
+        const int vst = i % 3;
+        // V has usually landed long ago: look at it first, so that nothing stands between P's arrival and the MMAs
+        ok = mbar_wait_warp(bar_v_full + 8 * vst, (i / 3) & 1, cta_abort, 114);
+        if (!ok) break;
         ok = mbar_wait_warp(bar_p_full + 8 * st, (i >> 1) & 1, cta_abort, 113);
         if (!ok) break;
         SQ_STAMP(i, 2);
-        const int vst = i % 3;
-        ok = mbar_wait_warp(bar_v_full + 8 * vst, (i / 3) & 1, cta_abort, 114);
-        if (!ok) break;
         tc_fence_after();
         const uint32_t p_tmem = tmem + st * kBlockN;
         const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(vst) * (L::kVBytes >> 4);
