@@ -91,21 +91,46 @@ class HostPrefillPipeline:
     such as the reference's, which keeps the KV cache on the host during prefill, cache_hub/flash_attn_cache.py):
     ``pipe(q_host, k_host, v_host, out_host)`` with q [1,N,Hq,D], k/v [1,N,Hkv,D] -> out [1,N,Hq*D].
 
-    K and V are uploaded and prepared once; Q is uploaded, prepared and attended in chunks of ``chunk_rows``
-    query rows (sqattn_prefill with q_row_offset) while the previous chunk's output travels back, so the H2D
-    copy, the kernels and the D2H copy overlap on three streams.  Results are identical to the one-shot
-    operator: chunks only partition the query rows."""
+    K goes first and whole (its centring needs the mean over the sequence); V and Q follow in chunks of query rows,
+    in sequence order: a chunk of rows needs only the V rows up to its own end (causal), so its V rows travel with
+    it, are prepared with it and the attention kernel (sqattn_prefill with q_row_offset) starts on the first chunk
+    while the rest of V and Q is still on the bus and earlier outputs travel back.  The first and the last chunk are
+    short, because the upload of the first and the download of the last cannot overlap with anything.  H2D copies,
+    kernels and D2H copies run on three streams.  Results are identical to the one-shot operator: chunks only
+    partition the query rows."""
 
     def __init__(self, bit8_window_sizes=0, bit4_window_sizes=0, sink_window_size=0, args=None, chunk_rows=4096,
-                 p_fp8_mode="off", device=None):
+                 p_fp8_mode="off", device=None, edge_rows=2048):
         self.bit8, self.bit4 = _normalise_windows(bit8_window_sizes, bit4_window_sizes)
         self.sink, self.args, self.chunk = sink_window_size, args, int(chunk_rows)
-        if self.chunk % 128:
-            raise ValueError("chunk_rows must be a multiple of 128")
+        self.edge = min(int(edge_rows), self.chunk)
+        if self.chunk % 128 or self.edge % 128 or self.edge <= 0:
+            raise ValueError("chunk_rows and edge_rows must be positive multiples of 128")
         self.fp8 = {"off": L.P_FP8_OFF, "all": L.P_FP8_ALL, "stage2": L.P_FP8_STAGE2}[p_fp8_mode]
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
         self._shape, self._buf = None, None
+
+    def _bounds(self, n):
+        """Row ranges of the chunks: a short first one, full chunks, a short last one."""
+        cuts = [0]
+        if n > 2 * self.chunk:
+            cuts.append(self.edge)
+            r = self.chunk
+            while r < n - self.chunk:
+                cuts.append(r)
+                r += self.chunk
+            cuts.append(r)
+            last = (n - self.edge) // 128 * 128   # a chunk starts on a multiple of 128 rows
+            if last > r:
+                cuts.append(last)
+        else:
+            r = self.chunk
+            while r < n:
+                cuts.append(r)
+                r += self.chunk
+        cuts.append(n)
+        return [(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1) if cuts[i + 1] > cuts[i]]
 
     def _buffers(self, n, hq, hkv, d, dtype):
         key = (n, hq, hkv, d, dtype)
@@ -113,9 +138,10 @@ class HostPrefillPipeline:
             dev, c = self.device, min(self.chunk, n)
             self._buf = {
                 "k": torch.empty(1, n, hkv, d, dtype=dtype, device=dev), "v": torch.empty(1, n, hkv, d, dtype=dtype, device=dev),
-                "k8": torch.empty(1, hkv, n, d, dtype=dtype, device=dev), "v8": torch.empty(1, hkv, n, d, dtype=torch.float16, device=dev),
+                # prepared K and V stay token-major, so that a chunk of V rows is one contiguous piece
+                "k8": torch.empty(1, n, hkv, d, dtype=dtype, device=dev), "v8": torch.empty(1, n, hkv, d, dtype=torch.float16, device=dev),
                 "q": [torch.empty(1, c, hq, d, dtype=dtype, device=dev) for _ in range(2)],
-                "q8": [torch.empty(1, hq, c, d, dtype=dtype, device=dev) for _ in range(2)],
+                "q8": [torch.empty(hq * c * d, dtype=dtype, device=dev) for _ in range(2)],
                 "o": [torch.empty(1, c, hq * d, dtype=torch.bfloat16, device=dev) for _ in range(2)],
             }
             self._shape = key
@@ -145,34 +171,31 @@ class HostPrefillPipeline:
         r8, r4 = per_head(self.bit8), per_head(self.bit4)
         with torch.cuda.stream(self.s_in):
             buf["k"].copy_(k_host, non_blocking=True)
-            buf["v"].copy_(v_host, non_blocking=True)
-            ev_kv = torch.cuda.Event()
-            ev_kv.record(self.s_in)
-        cur.wait_event(ev_kv)
-        ops.prep_qkv(None, buf["k"], buf["v"], qk_qtype=a.qk_qtype, v_qtype=a.v_qtype, skip_bit4=True,
-                     out={"k8": buf["k8"], "v8": buf["v8"]})
+            ev_k = torch.cuda.Event()
+            ev_k.record(self.s_in)
+        cur.wait_event(ev_k)
+        ops.prep_qkv(None, buf["k"], None, qk_qtype=a.qk_qtype, v_qtype=a.v_qtype, skip_bit4=True, kv_out_nhd=True,
+                     out={"k8": buf["k8"]})
         q_free = [None, None]   # compute has finished reading q buffer s
         o_free = [None, None]   # the D2H copy has finished reading output buffer s
-        for ci, r0 in enumerate(range(0, n, self.chunk)):
-            r1 = min(n, r0 + self.chunk)
+        for ci, (r0, r1) in enumerate(self._bounds(n)):
             rows, s = r1 - r0, ci & 1
             with torch.cuda.stream(self.s_in):
                 if q_free[s] is not None:
                     self.s_in.wait_event(q_free[s])
+                buf["v"][:, r0:r1].copy_(v_host[:, r0:r1], non_blocking=True)
                 buf["q"][s][:, :rows].copy_(q_host[:, r0:r1], non_blocking=True)
                 ev_q = torch.cuda.Event()
                 ev_q.record(self.s_in)
             cur.wait_event(ev_q)
             if o_free[s] is not None:
                 cur.wait_event(o_free[s])
-            q8 = buf["q8"][s][:, :, :rows]
-            if rows != buf["q8"][s].shape[2]:
-                q8 = torch.empty(1, hq, rows, d, dtype=q_host.dtype, device=self.device)
-            ops.prep_qkv(buf["q"][s][:, :rows], None, None, qk_qtype=a.qk_qtype, v_qtype=a.v_qtype, skip_bit4=True,
-                         out={"q8": q8})
+            q8 = buf["q8"][s][: hq * rows * d].view(1, hq, rows, d)
+            ops.prep_qkv(buf["q"][s][:, :rows], None, buf["v"][:, r0:r1], qk_qtype=a.qk_qtype, v_qtype=a.v_qtype,
+                         skip_bit4=True, kv_out_nhd=True, out={"q8": q8, "v8": buf["v8"][:, r0:r1]})
             o = buf["o"][s][:, :rows]
             ops.prefill(q8, buf["k8"], q8, buf["k8"], buf["v8"], mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4,
-                        sink=self.sink, layout="HND", p_fp8_mode=self.fp8, q_is_scaled=True,
+                        sink=self.sink, layout="HND", kv_layout="NHD", p_fp8_mode=self.fp8, q_is_scaled=True,
                         out=o.view(1, rows, hq, d), out_layout="NHD", q_row_offset=r0)
             ev_c = torch.cuda.Event()
             ev_c.record(cur)

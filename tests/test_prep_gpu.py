@@ -91,11 +91,13 @@ def test_host_pipeline_matches_operator():
         qk_qtype, v_qtype, use_relative_distance = "int", "int", True
 
     ref = mp_triton_wrapper(0, [0.2] * hq, [0.4] * hq, 256, Args())(Layer(), q.cuda(), k.cuda(), v.cuda(), None)
-    pipe = HostPrefillPipeline([0.2] * hq, [0.4] * hq, 256, Args(), chunk_rows=512)
-    for _ in range(2):   # buffers are reused across calls
-        out = pipe(q.pin_memory(), k.pin_memory(), v.pin_memory())
-        torch.cuda.synchronize()
-        assert out.is_pinned() and torch.equal(out, ref.cpu())
+    for edge in (512, 128):   # short first and last chunks
+        pipe = HostPrefillPipeline([0.2] * hq, [0.4] * hq, 256, Args(), chunk_rows=512, edge_rows=edge)
+        assert pipe._bounds(n)[0] == (0, edge) and pipe._bounds(n)[-1][1] == n
+        for _ in range(2):   # buffers are reused across calls
+            out = pipe(q.pin_memory(), k.pin_memory(), v.pin_memory())
+            torch.cuda.synchronize()
+            assert out.is_pinned() and torch.equal(out, ref.cpu())
     with pytest.raises(ValueError):
         pipe(q, k, v)   # pageable host memory
 
