@@ -32,7 +32,7 @@ __device__ __forceinline__ void retrieve_select_body(const RetrieveParams& p, co
   __shared__ double red_v[32];
   __shared__ int red_i[32];
   __shared__ int sel_list[kRetMaxClusters];
-  __shared__ int n_sel, total_tok, warp_sums[32];
+  __shared__ int n_sel, total_tok, win_s, warp_sums[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = p.num_clusters, D = p.d;
   const uint16_t* q = reinterpret_cast<const uint16_t*>(p.q) + static_cast<long long>(g) * p.groups * D;
@@ -49,43 +49,98 @@ __device__ __forceinline__ void retrieve_select_body(const RetrieveParams& p, co
   for (int w = tid; w < words; w += blockDim.x) bitmap[w] = 0u;
   if (tid == 0) { n_sel = 0; total_tok = 0; }
   __syncthreads();
-  for (int c = tid; c < K; c += blockDim.x) {
-    double s = 0.0;
-    for (int d = 0; d < D; ++d) s += static_cast<double>(to_f32<BF16>(cent[static_cast<long long>(c) * D + d])) * static_cast<double>(q_mean[d]);
-    scores[c] = (csize[c] > 0) ? s : -1.0 / 0.0;  // empty clusters are never taken
-  }
-  __syncthreads();
-  // greedy selection: best remaining cluster until the budget is covered
-  for (int iter = 0; iter < K; ++iter) {
-    if (total_tok >= p.budget) break;
-    double bv = -1.0 / 0.0;
-    int bi = 0x7fffffff;
-    for (int c = tid; c < K; c += blockDim.x) {
-      const double v = scores[c];
-      if (v > bv || (v == bv && c < bi && v != -1.0 / 0.0)) { bv = v; bi = c; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-      const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
-    __syncthreads();
-    if (tid == 0) {
-      double v = red_v[0];
-      int i = red_i[0];
-      for (int w = 1; w < (blockDim.x >> 5); ++w)
-        if (red_v[w] > v || (red_v[w] == v && red_i[w] < i)) { v = red_v[w]; i = red_i[w]; }
-      if (v == -1.0 / 0.0 || i == 0x7fffffff) {
-        total_tok = 0x7fffffff;  // nothing left
-      } else {
-        sel_list[n_sel++] = i;
-        total_tok += csize[i];
-        scores[i] = -1.0 / 0.0;
+  // Scores: D/8 lanes per centroid row, 16-byte loads (a warp reads whole rows, coalesced), four rows per lane in
+  // flight; each lane adds its eight products in index order, the lanes' sums are combined pairwise in a fixed
+  // order, so a score does not depend on timing (and centroids with identical rows get identical scores).
+  {
+    const int lanes_per_row = D / 8, rows_per_warp = 32 / lanes_per_row;
+    const int sub = lane % lanes_per_row, rslot = lane / lanes_per_row;
+    constexpr int kInFlight = 4;
+    double qd[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qd[e] = static_cast<double>(q_mean[sub * 8 + e]);
+    const int stride = (blockDim.x >> 5) * rows_per_warp;
+    for (int c0 = warp * rows_per_warp; c0 < K; c0 += kInFlight * stride) {
+      uint4 raw[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int c = c0 + u * stride + rslot;
+        raw[u] = (c < K) ? *reinterpret_cast<const uint4*>(cent + static_cast<long long>(c) * D + sub * 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int c = c0 + u * stride + rslot;
+        float f[8];
+        unpack8<BF16>(raw[u], f);
+        double sc = 0.0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc += static_cast<double>(f[e]) * qd[e];
+        for (int o = lanes_per_row >> 1; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+        if (c < K && sub == 0) scores[c] = (csize[c] > 0) ? sc : -1.0 / 0.0;  // empty clusters are never taken
       }
     }
-    __syncthreads();
   }
+  __syncthreads();
+  // Greedy selection: the best remaining cluster until the budget is covered (ties: lowest index).  The first
+  // kSelThreads threads do it (a barrier of 256 threads is cheaper than one of 1024, and there is one pair per
+  // selected cluster): thread t owns the clusters t, t + kSelThreads, ... and keeps the best of them in registers; a
+  // round is a warp arg-max by shuffles, an arg-max over the warps' results by warp 0, and a refresh by the one
+  // thread that owned the winner.
+  constexpr int kSelThreads = 256;
+  if (tid < kSelThreads) {
+    auto better = [](double v, int i, double bv, int bi) { return v > bv || (v == bv && i < bi); };
+    auto sel_sync = [] { asm volatile("bar.sync 1, 256;" ::: "memory"); };
+    double my_v = -1.0 / 0.0;
+    int my_i = 0x7fffffff;
+    auto refresh = [&]() {
+      my_v = -1.0 / 0.0; my_i = 0x7fffffff;
+      for (int c = tid; c < K; c += kSelThreads) {
+        const double v = scores[c];
+        if (v != -1.0 / 0.0 && better(v, c, my_v, my_i)) { my_v = v; my_i = c; }
+      }
+    };
+    refresh();
+    constexpr int nwarps = kSelThreads / 32;
+    for (int iter = 0; iter < K; ++iter) {
+      if (total_tok >= p.budget) break;
+      double bv = my_v;
+      int bi = my_i;
+      for (int o = 16; o > 0; o >>= 1) {
+        const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+      sel_sync();
+      if (warp == 0) {
+        double v = lane < nwarps ? red_v[lane] : -1.0 / 0.0;
+        int i = lane < nwarps ? red_i[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+          const double ov = __shfl_xor_sync(0xffffffffu, v, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+          if (better(ov, oi, v, i)) { v = ov; i = oi; }
+        }
+        if (lane == 0) {
+          if (v == -1.0 / 0.0 || i == 0x7fffffff) {
+            total_tok = 0x7fffffff;  // nothing left
+            win_s = -1;
+          } else {
+            sel_list[n_sel++] = i;
+            total_tok += csize[i];
+            win_s = i;               // the winner, for its owner
+          }
+        }
+      }
+      sel_sync();
+      // (win_s is rewritten only behind the next round's first barrier, which no thread passes before it has read it)
+      const int won = win_s;
+      if (won >= 0 && won % kSelThreads == tid) {
+        scores[won] = -1.0 / 0.0;
+        refresh();
+      }
+    }
+  }
+  __syncthreads();
   // members of the selected clusters -> bitmap over token positions
   const int ns = n_sel;
   for (int s = warp; s < ns; s += (blockDim.x >> 5)) {

@@ -793,7 +793,7 @@ int sqattn_retrieve_select(const void* q, const void* centroids, int32_t dtype, 
                            int32_t* out_idx, int32_t* out_count, int32_t cap, int32_t tail_start, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!q || !centroids || !cluster_size || !clusters || !out_idx || !out_count) return fail(SQATTN_ERR_INVALID_ARG, "null pointer");
-  if (head_dim > 128 || head_dim % 8) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: at most 128, multiple of 8", head_dim);
+  if (head_dim != 64 && head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: 64 or 128", head_dim);
   if (num_clusters <= 0 || num_clusters > kRetMaxClusters) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d clusters supported", kRetMaxClusters);
   if (num_tokens <= 0 || num_tokens > kRetMaxTokens) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d tokens supported", kRetMaxTokens);
   if (groups_kv <= 0 || heads_per_group <= 0 || budget <= 0 || cap <= 0 || max_cluster_size <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
@@ -834,7 +834,7 @@ int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, 
                           int32_t heads_per_group, int32_t head_dim, int32_t budget, int32_t cap, sqattn_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (!items || num_items <= 0) return fail(SQATTN_ERR_INVALID_ARG, "no items");
-  if (head_dim > 128 || head_dim % 8) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: at most 128, multiple of 8", head_dim);
+  if (head_dim != 64 && head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: 64 or 128", head_dim);
   if (groups_kv <= 0 || heads_per_group <= 0 || budget <= 0 || cap <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
   for (int first = 0; first < num_items; first += kRetMaxBatch) {
     const int n = num_items - first < kRetMaxBatch ? num_items - first : kRetMaxBatch;
