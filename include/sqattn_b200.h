@@ -152,6 +152,18 @@ int sqattn_k_column_sums(const sqattn_tensor* k, int32_t batch, int32_t num_kv_h
 
 struct sqattn_peer_merge_args;
 
+/* Keys and values addressed through an index list instead of a contiguous cache (the attention over the tokens a
+ * clustered cache retrieved, without first packing them): key j of (sequence b, KV head h) is row idx[(b * Hkv + h)
+ * * cap + j] of the 16-bit matrices k_rows[b * Hkv + h] / v_rows[b * Hkv + h] (device arrays of device pointers),
+ * rows row_stride elements apart.  No counterpart in the reference. */
+typedef struct sqattn_decode_gather {
+  const int32_t* idx;            /* device, [B * Hkv, cap] */
+  int32_t cap;
+  const void* const* k_rows;     /* device, [B * Hkv] */
+  const void* const* v_rows;     /* device, [B * Hkv] */
+  int64_t row_stride;            /* elements, a multiple of 8 */
+} sqattn_decode_gather;
+
 typedef struct {
   sqattn_tensor q;         /* [B, Hq, 1, D] */
   sqattn_tensor k, v;      /* [B, Hkv, kv_capacity, D] */
@@ -182,6 +194,10 @@ typedef struct {
   const struct sqattn_peer_merge_args* peer;
   int32_t head_dim_og;     /* as in sqattn_prefill_args: the un-padded head_dim the softmax scale is taken from when
                               q_is_scaled == 0 (attn_triton_decode.py:254-271); 0 = head_dim */
+  /* When set, k and v are ignored and the keys and values are the listed rows (kv_len = the list capacity to plan
+   * for, kv_lens / kv_lens_device = the list lengths); the rows are copied into shared memory by 16-byte
+   * asynchronous copies instead of tiled TMA loads.  reference_tail must be 0. */
+  const sqattn_decode_gather* gather;
 } sqattn_decode_args;
 
 /* Replaces attn_unified's decode branch + _attn_decode_fwd, sqattn/attn_triton_decode.py:175-241,
@@ -273,7 +289,7 @@ typedef struct sqattn_retrieve_item {
   const void* k_src;             /* [G, tokens, D] through the strides below (elements) */
   const void* v_src;
   int64_t src_group_stride, src_row_stride;
-  void* k_dst;                   /* [G, cap, D] */
+  void* k_dst;                   /* [G, cap, D]; k_dst == v_dst == NULL for every item: select only, no packing */
   void* v_dst;
   int32_t tail_start;            /* as in sqattn_retrieve_select */
   /* block-hybrid caches (cache_hub/cache.py keeps part of the KV on the host): tokens from split_row on are read

@@ -69,8 +69,13 @@ class DecodeArgs(C.Structure):
         ("num_splits", C.c_int32), ("reference_tail", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("partial_o", C.c_void_p), ("partial_lse", C.c_void_p), ("kv_lens_device", C.c_void_p), ("peer", C.c_void_p),
-        ("head_dim_og", C.c_int32),
+        ("head_dim_og", C.c_int32), ("gather", C.c_void_p),
     ]
+
+
+class DecodeGather(C.Structure):
+    _fields_ = [("idx", C.c_void_p), ("cap", C.c_int32), ("k_rows", C.c_void_p), ("v_rows", C.c_void_p),
+                ("row_stride", C.c_int64)]
 
 
 # every symbol include/sqattn_b200.h declares: (name, restype, argtypes)

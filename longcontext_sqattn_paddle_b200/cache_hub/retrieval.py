@@ -169,10 +169,17 @@ class RaggedClusteredDecoder:
         self.v_sel = torch.empty(b * self.hkv, 1, self.cap, self.d, dtype=dt, device=dev)
         self._q = None        # persistent copy of the step's queries: the item table below points into it
         self._items, self._state = None, None
+        self._rows = None     # device arrays of the K / V base pointers of every (sequence, KV head), for in-place attention
+
+    def _in_place(self) -> bool:
+        """The selected rows can be attended where they lie when every cache is wholly on the device and all share a
+        row stride (block-hybrid caches go through the packing kernel, which also reads the host part)."""
+        return all(c.key_host is None for c in self.caches)
 
     def _table(self, hq: int):
         """One sqattn_retrieve_item per sequence; every pointer in it stays valid for the decoder's lifetime."""
         b = len(self.caches)
+        in_place = self._in_place()
         self._q = torch.empty(b, hq, 1, self.d, dtype=self.caches[0].key.dtype, device=self.idx.device)
         items = (L.RetrieveItem * b)()
         for i, c in enumerate(self.caches):
@@ -187,13 +194,21 @@ class RaggedClusteredDecoder:
             if c.key_host is not None:      # hybrid layout: rows from `split` on are read from pinned host memory
                 it.split_row, it.k_src2, it.v_src2 = c.split, c.key_host.data_ptr(), c.value_host.data_ptr()
                 it.src2_group_stride = c.key_host.stride(0)
-            it.k_dst = self.k_sel[i * self.hkv:(i + 1) * self.hkv].data_ptr()
-            it.v_dst = self.v_sel[i * self.hkv:(i + 1) * self.hkv].data_ptr()
+            if not in_place:   # no destination in any item: sqattn_retrieve_batch only selects
+                it.k_dst = self.k_sel[i * self.hkv:(i + 1) * self.hkv].data_ptr()
+                it.v_dst = self.v_sel[i * self.hkv:(i + 1) * self.hkv].data_ptr()
         self._items = items
+        if in_place:
+            esz = self.caches[0].key.element_size()
+            kp = [c.key.data_ptr() + h * c.key.stride(0) * esz for c in self.caches for h in range(self.hkv)]
+            vp = [c.value.data_ptr() + h * c.value.stride(0) * esz for c in self.caches for h in range(self.hkv)]
+            dev = self.idx.device
+            self._rows = (torch.tensor(kp, dtype=torch.int64, device=dev), torch.tensor(vp, dtype=torch.int64, device=dev))
 
     def step(self, q: torch.Tensor, out_dtype=None) -> torch.Tensor:
-        """Four launches and no host synchronisation: select (all sequences), gather (all keys and values), split-KV
-        decode with the retrieved counts read on the device, merge."""
+        """Three launches and no host synchronisation: select (all sequences), split-KV decode that copies the listed
+        rows from the caches into shared memory itself (lengths read on the device), merge.  Block-hybrid caches add a
+        launch that packs the rows (device and host part) first."""
         b, hq, _, d = q.shape
         groups = hq // self.hkv
         state = tuple((c.tokens, c.clustered, c.max_cluster_size, c.clusters.data_ptr()) for c in self.caches)
@@ -206,8 +221,12 @@ class RaggedClusteredDecoder:
         L.check(L.lib.sqattn_retrieve_batch(self._items, b, _dt(q.dtype), self.hkv, groups, d, self.budget, self.cap,
                                             _stream()))
         qv = self._q.view(b * self.hkv, groups, 1, d)
-        o = ops.decode(qv, self.k_sel, self.v_sel, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8, kv_len=self.cap,
-                       kv_lens_device=self.count.view(-1))
+        if self._in_place():
+            o = ops.decode_gather(qv, self.idx.view(b * self.hkv, self.cap), self.count.view(-1), self._rows[0], self._rows[1],
+                                  d, q.dtype, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8)
+        else:
+            o = ops.decode(qv, self.k_sel, self.v_sel, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8, kv_len=self.cap,
+                           kv_lens_device=self.count.view(-1))
         return o.view(b, hq, 1, d)
 
     def step_unbatched(self, q: torch.Tensor, out_dtype=None) -> torch.Tensor:

@@ -2,7 +2,9 @@
 // full bandwidth.  One CTA handles one (sequence, KV head, key range) work item for ALL query heads of
 // the KV group, so the group's K/V are read once (the reference reads them once per query head,
 // sqattn/attn_triton_decode.py:204-241).
-//   warp 4      TMA producer: 64-key K and V tiles into a 3-stage shared-memory ring (128-byte swizzle)
+//   warp 4      TMA producer: 64-key K and V tiles into a 3-stage shared-memory ring (128-byte swizzle); when the
+//               keys are an index list into a cache, the same warp copies the listed rows into the same layout
+//               with 16-byte asynchronous copies (two rows of K and V per lane and tile)
 //   warps 0..3  16 keys of every tile each: S = q K^T and O += P V on mma.sync m16n8k16 (query heads padded
 //               to the 16-row M dimension), warp-shuffle row max / sum, private online-softmax state;
 //               the four states are merged through shared memory at the end of the item.
@@ -32,7 +34,22 @@ struct DecodeParams {
   int lens[kDecMaxBatch];
   const int* lens_dev;  // when set, the lengths are read from the device at run time (lens[] holds the planned capacity)
   int item_prefix[kDecMaxBatch + 1];  // first work item of each sequence
+  // Keys and values through an index list (the tokens a clustered cache retrieved): key j of (sequence, KV head) is
+  // row gather_idx[(bi * hkv + kvh) * gather_cap + j] of gather_k / gather_v [bi * hkv + kvh]; nullptr: the tiled caches
+  const int* gather_idx;
+  const uint8_t* const* gather_k;
+  const uint8_t* const* gather_v;
+  long long gather_row_stride;  // elements
+  int gather_cap;
 };
+
+// 16-byte asynchronous copy global -> shared, and an arrival on `bar` once all of this thread's copies have landed
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -137,13 +154,52 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
-    for (int i = 0; i < kDecStages; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 4); }
+    // a stage is full after the producer's one arrival + its bytes (TMA), or after all 32 lanes' copies (index list)
+    for (int i = 0; i < kDecStages; ++i) { mbar_init(bar_full + 8 * i, p.gather_idx ? 32 : 1); mbar_init(bar_empty + 8 * i, 4); }
     fence_barrier_init();
     fence_proxy_async();
   }
   __syncthreads();
 
-  if (warp == 4) {
+  if (warp == 4 && p.gather_idx) {
+    const long long grp = static_cast<long long>(bi) * p.hkv + kvh;
+    const int* idx = p.gather_idx + grp * p.gather_cap;
+    const uint8_t* kb = p.gather_k[grp];
+    const uint8_t* vb = p.gather_v[grp];
+    bool ok = true;
+    // the list entries of a tile are fetched one tile ahead, so that their latency hides behind the wait for a stage
+    auto fetch = [&](int t, int (&tok)[2]) {
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int key = key_begin + t * kDecTile + lane + 32 * rr;
+        tok[rr] = (t < ntiles && key < key_end) ? idx[key] : -1;   // rows past the end are never read as data
+      }
+    };
+    int tok[2], nxt[2];
+    fetch(0, tok);
+    for (int t = 0; ok && t < ntiles; ++t) {
+      const int st = t % kDecStages;
+      fetch(t + 1, nxt);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, ((t / kDecStages) & 1) ^ 1, cta_abort, 201));
+      if (!ok) break;
+      const uint32_t k_tile = sbase + st * L::kStageBytes, v_tile = k_tile + L::kTileBytes;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int r = lane + 32 * rr;
+        if (tok[rr] >= 0) {
+          const long long off = static_cast<long long>(tok[rr]) * p.gather_row_stride * 2;
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) {
+            cp_async_16(k_tile + tile_off(r, c), kb + off + c * 16);
+            cp_async_16(v_tile + tile_off(r, c), vb + off + c * 16);
+          }
+        }
+      }
+      cp_async_arrive(bar_full + 8 * st);
+      tok[0] = nxt[0]; tok[1] = nxt[1];
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp is in flight when the CTA winds down
+  } else if (warp == 4) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
       bool ok = true;

@@ -265,6 +265,16 @@ int plan_decode(const sqattn_decode_args* a, DecodePlan* pl) {
   if (a->head_dim_og < 0 || a->head_dim_og > a->head_dim)
     return fail(SQATTN_ERR_INVALID_ARG, "head_dim_og %d must lie in [0, head_dim %d]", a->head_dim_og, a->head_dim);
   if (a->kv_lens_device && a->kv_lens) return fail(SQATTN_ERR_INVALID_ARG, "kv_lens and kv_lens_device are exclusive: device lengths are planned for kv_len");
+  if (a->gather) {
+    const sqattn_decode_gather* g = a->gather;
+    if (!g->idx || !g->k_rows || !g->v_rows) return fail(SQATTN_ERR_INVALID_ARG, "gather: null pointer");
+    if (g->cap <= 0 || g->row_stride < a->head_dim || g->row_stride % 8)
+      return fail(SQATTN_ERR_INVALID_ARG, "gather: cap %d must be positive, row_stride %lld a multiple of 8 not below head_dim", g->cap, static_cast<long long>(g->row_stride));
+    if (a->reference_tail) return fail(SQATTN_ERR_INVALID_ARG, "gather: reference_tail is not supported");
+    for (int b = 0; b < a->batch; ++b)
+      if ((a->kv_lens ? a->kv_lens[b] : a->kv_len) > g->cap)
+        return fail(SQATTN_ERR_INVALID_ARG, "gather: sequence %d has more keys than the index list holds (%d)", b, g->cap);
+  }
   long long total_tiles = 0;
   for (int b = 0; b < a->batch; ++b) {
     const int len = a->kv_lens ? a->kv_lens[b] : a->kv_len;
@@ -331,10 +341,20 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   // the maps cover the whole cache capacity of each sequence; lengths are enforced in the kernel
   int cap = 1;
   for (int b = 0; b < a->batch; ++b) cap = pl.lens[b] > cap ? pl.lens[b] : cap;
-  if ((rc = make_tmap_bhnd(&tk, a->k.ptr, a->dtype, a->k.stride_b, a->k.stride_h, a->k.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "k"))) return rc;
-  if ((rc = make_tmap_bhnd(&tv, a->v.ptr, a->dtype, a->v.stride_b, a->v.stride_h, a->v.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "v"))) return rc;
+  if (a->gather) {   // the listed rows are copied by the producer warp itself: the maps are never used
+    memset(&tk, 0, sizeof(tk));
+    memset(&tv, 0, sizeof(tv));
+  } else {
+    if ((rc = make_tmap_bhnd(&tk, a->k.ptr, a->dtype, a->k.stride_b, a->k.stride_h, a->k.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "k"))) return rc;
+    if ((rc = make_tmap_bhnd(&tv, a->v.ptr, a->dtype, a->v.stride_b, a->v.stride_h, a->v.stride_n, a->batch, a->num_kv_heads, cap, D, kDecTile, "v"))) return rc;
+  }
   DecodeParams p;
   memset(&p, 0, sizeof(p));
+  if (a->gather) {
+    p.gather_idx = a->gather->idx; p.gather_cap = a->gather->cap; p.gather_row_stride = a->gather->row_stride;
+    p.gather_k = reinterpret_cast<const uint8_t* const*>(a->gather->k_rows);
+    p.gather_v = reinterpret_cast<const uint8_t* const*>(a->gather->v_rows);
+  }
   p.q = static_cast<const uint8_t*>(a->q.ptr); p.q_sb = a->q.stride_b; p.q_sh = a->q.stride_h;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   const size_t rows = static_cast<size_t>(pl.total_items > 0 ? pl.total_items : 1) * a->num_q_heads;
@@ -577,10 +597,10 @@ int sqattn_decode(const sqattn_decode_args* a, sqattn_stream_t stream_) {
   DecodePlan pl;
   int rc = plan_decode(a, &pl);
   if (rc) return rc;
-  if (!a->q.ptr || !a->k.ptr || !a->v.ptr) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
+  if (!a->q.ptr || (!a->gather && (!a->k.ptr || !a->v.ptr))) return fail(SQATTN_ERR_INVALID_ARG, "null tensor pointer");
   if (!a->partial_o && !a->o.ptr && !a->peer) return fail(SQATTN_ERR_INVALID_ARG, "null output pointer");
   if (a->partial_o && !a->partial_lse) return fail(SQATTN_ERR_INVALID_ARG, "partial_lse missing");
-  if (!aligned16(a->k) || !aligned16(a->v)) return fail(SQATTN_ERR_INVALID_ARG, "k/v need 16-byte alignment");
+  if (!a->gather && (!aligned16(a->k) || !aligned16(a->v))) return fail(SQATTN_ERR_INVALID_ARG, "k/v need 16-byte alignment");
   if ((reinterpret_cast<uintptr_t>(a->q.ptr) % 4) || (a->q.stride_h % 2) || (a->q.stride_b % 2)) return fail(SQATTN_ERR_INVALID_ARG, "q needs 4-byte alignment");
   const size_t need = decode_ws_bytes(a, pl);
   if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) % 256))
@@ -836,6 +856,9 @@ int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, 
   if (!items || num_items <= 0) return fail(SQATTN_ERR_INVALID_ARG, "no items");
   if (head_dim != 64 && head_dim != 128) return fail(SQATTN_ERR_UNSUPPORTED, "head_dim %d: 64 or 128", head_dim);
   if (groups_kv <= 0 || heads_per_group <= 0 || budget <= 0 || cap <= 0) return fail(SQATTN_ERR_INVALID_ARG, "bad sizes");
+  // select only (the caller attends the listed rows in place): no item has a destination
+  bool pack = false;
+  for (int i = 0; i < num_items; ++i) pack = pack || items[i].k_dst || items[i].v_dst;
   for (int first = 0; first < num_items; first += kRetMaxBatch) {
     const int n = num_items - first < kRetMaxBatch ? num_items - first : kRetMaxBatch;
     RetrieveBatch rb;
@@ -845,8 +868,8 @@ int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, 
     size_t smem = 0;
     for (int i = 0; i < n; ++i) {
       const sqattn_retrieve_item& it = items[first + i];
-      if (!it.q || !it.centroids || !it.cluster_size || !it.clusters || !it.out_idx || !it.out_count || !it.k_src || !it.v_src ||
-          !it.k_dst || !it.v_dst)
+      if (!it.q || !it.centroids || !it.cluster_size || !it.clusters || !it.out_idx || !it.out_count ||
+          (pack && (!it.k_src || !it.v_src || !it.k_dst || !it.v_dst)))
         return fail(SQATTN_ERR_INVALID_ARG, "retrieve item %d: null pointer", first + i);
       if (it.num_clusters <= 0 || it.num_clusters > kRetMaxClusters) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d clusters supported", kRetMaxClusters);
       if (it.num_tokens <= 0 || it.num_tokens > kRetMaxTokens) return fail(SQATTN_ERR_UNSUPPORTED, "1..%d tokens supported", kRetMaxTokens);
@@ -877,6 +900,7 @@ int sqattn_retrieve_batch(const sqattn_retrieve_item* items, int32_t num_items, 
       retrieve_select_batch_kernel<false><<<sgrid, 1024, smem, stream>>>(rb);
     }
     SQ_CUDA(cudaGetLastError());
+    if (!pack) continue;
     const dim3 ggrid(elementwise_grid(static_cast<long long>(cap) * (head_dim / 8), 256), groups_kv, 2 * n);
     gather_rows_batch_kernel<<<ggrid, 256, 0, stream>>>(gb, cap, head_dim);
     SQ_CUDA(cudaGetLastError());

@@ -254,6 +254,40 @@ def decode(q, k, v, *, layout: str = "HND", out_dtype=torch.float16, return_lse:
     return (out, lse) if return_lse else out
 
 
+def decode_gather(q, idx, counts, k_rows, v_rows, row_stride: int, kv_dtype, *, out_dtype=torch.float16,
+                  p_fp8: bool = False, q_is_scaled: bool = False, num_kv_heads: int = 1):
+    """sqattn_decode over listed rows (sqattn_decode_args.gather): q [B,Hq,1,D]; key j of (sequence b, KV head h) is row
+    idx[b*Hkv+h, j] of the matrix at k_rows[b*Hkv+h] / v_rows[b*Hkv+h] (int64 device tensors of device pointers), rows
+    ``row_stride`` elements apart; counts (int32 [B] on the device) are the list lengths, idx.shape[1] the capacity the
+    key ranges are planned for.  No host synchronisation."""
+    _require_cuda(q, idx, counts, k_rows, v_rows)
+    poll_device_status(q.device)
+    b, hq, one, d = q.shape
+    assert one == 1 and idx.dtype == torch.int32 and idx.is_contiguous() and idx.shape[0] == b * num_kv_heads
+    assert counts.dtype == torch.int32 and counts.numel() == b
+    assert k_rows.dtype == torch.int64 and v_rows.dtype == torch.int64 and k_rows.numel() == b * num_kv_heads == v_rows.numel()
+    g = L.DecodeGather()
+    g.idx, g.cap, g.k_rows, g.v_rows, g.row_stride = idx.data_ptr(), idx.shape[1], k_rows.data_ptr(), v_rows.data_ptr(), int(row_stride)
+    a = L.DecodeArgs()
+    a.q = _view(q, "HND")
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim = b, hq, num_kv_heads, d
+    a.kv_len = idx.shape[1]
+    a.dtype, a.p_fp8, a.q_is_scaled = _dt(kv_dtype), int(p_fp8), int(q_is_scaled)
+    a.kv_lens_device = counts.data_ptr()
+    a.gather = C.addressof(g)
+    out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
+    a.o = _view(out, "HND")
+    a.o_dtype = _dt(out_dtype)
+    need = L.lib.sqattn_decode_workspace_bytes(C.byref(a))
+    if need == 0:  # the plan was rejected: let the entry point report why
+        L.check(L.lib.sqattn_decode(C.byref(a), _stream()))
+        raise ValueError("sqattn_decode: invalid arguments")
+    ws = _workspace(need, q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need
+    L.check(L.lib.sqattn_decode(C.byref(a), _stream()))
+    return out
+
+
 def decode_merge(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype=torch.float16, return_lse: bool = False):
     """sqattn_decode_merge: part_o [P, rows, D] fp32, part_lse [P, rows] fp32 -> O [rows, D]."""
     _require_cuda(part_o, part_lse)

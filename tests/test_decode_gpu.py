@@ -111,3 +111,37 @@ def test_decode_reference_golden(golden_dir, name, fp8):
     go, gl = torch.from_numpy(z["o_fp8" if fp8 else "o"]), torch.from_numpy(z["lse_fp8" if fp8 else "lse"])
     assert (o.float().cpu() - go.float()).abs().max().item() < 8e-3
     assert (lse.cpu() - gl).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_decode_over_listed_rows_equals_decode_over_packed_copies(dtype, fp8):
+    """sqattn_decode_args.gather: attending rows of a cache through an index list gives the bits of attending a
+    packed copy of those rows (the kernel's arithmetic is the same, only the producer differs); ragged list lengths,
+    one of them empty-tailed inside a 64-key tile, caches with different lengths and a strided row layout."""
+    from longcontext_sqattn_paddle_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    b, groups, d, cap = 5, 4, 128, 1408
+    lens_cache = [3000, 777, 5000, 1500, 2048]
+    counts = [1408, 300, 1000, 65, 640]
+    caches = [(torch.randn(n, 2 * d, generator=g).to(dtype).cuda(), torch.randn(n, 2 * d, generator=g).to(dtype).cuda())
+              for n in lens_cache]          # rows 2*d apart: the first d columns are the row
+    idx = torch.zeros(b, cap, dtype=torch.int32)
+    for i, (n, c) in enumerate(zip(lens_cache, counts)):
+        idx[i, :c] = torch.sort(torch.randperm(n, generator=g)[:c]).values.to(torch.int32)
+        idx[i, c:] = 2 ** 30                # never read
+    idx = idx.cuda()
+    cnt = torch.tensor(counts, dtype=torch.int32, device="cuda")
+    q = torch.randn(b, groups, 1, d, generator=g).to(dtype).cuda()
+    k_rows = torch.tensor([k.data_ptr() for k, _ in caches], dtype=torch.int64, device="cuda")
+    v_rows = torch.tensor([v.data_ptr() for _, v in caches], dtype=torch.int64, device="cuda")
+    out = ops.decode_gather(q, idx, cnt, k_rows, v_rows, 2 * d, dtype, out_dtype=dtype, p_fp8=fp8)
+    k_sel = torch.zeros(b, 1, cap, d, dtype=dtype, device="cuda")
+    v_sel = torch.zeros(b, 1, cap, d, dtype=dtype, device="cuda")
+    for i, c in enumerate(counts):
+        rows = idx[i, :c].long()
+        k_sel[i, 0, :c] = caches[i][0][rows, :d]
+        v_sel[i, 0, :c] = caches[i][1][rows, :d]
+    ref = ops.decode(q, k_sel, v_sel, out_dtype=dtype, p_fp8=fp8, kv_len=cap, kv_lens_device=cnt)
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, ref)
