@@ -83,51 +83,61 @@ __device__ __forceinline__ void retrieve_select_body(const RetrieveParams& p, co
   __syncthreads();
   // Greedy selection: the best remaining cluster until the budget is covered (ties: lowest index).  The first
   // kSelThreads threads do it (a barrier of 256 threads is cheaper than one of 1024, and there is one pair per
-  // selected cluster): thread t owns the clusters t, t + kSelThreads, ... and keeps the best of them in registers; a
-  // round is a warp arg-max by shuffles, an arg-max over the warps' results by warp 0, and a refresh by the one
-  // thread that owned the winner.
+  // selected cluster).  The fp64 scores are first replaced, in place, by 64-bit integers of the same order (0 = taken
+  // or empty, below every real score), so that an arg-max over a warp is three warp-wide integer reductions (high
+  // word, low word among the lanes that hold the high word, lowest index among the lanes that hold both).  Thread t
+  // owns the clusters t, t + kSelThreads, ... and keeps the best of them in registers; a round is that arg-max per
+  // warp, the same over the warps' results by warp 0, and a refresh by the one thread that owned the winner.
   constexpr int kSelThreads = 256;
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(scores);
+  for (int c = tid; c < K; c += blockDim.x) {
+    const double v = scores[c];
+    const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(v));
+    keys[c] = (v == -1.0 / 0.0) ? 0ull : ((bits >> 63) ? ~bits : (bits | 0x8000000000000000ull));
+  }
+  __syncthreads();
   if (tid < kSelThreads) {
-    auto better = [](double v, int i, double bv, int bi) { return v > bv || (v == bv && i < bi); };
+    unsigned long long* red_k = reinterpret_cast<unsigned long long*>(red_v);
     auto sel_sync = [] { asm volatile("bar.sync 1, 256;" ::: "memory"); };
-    double my_v = -1.0 / 0.0;
+    auto warp_argmax = [](unsigned long long& k, int& i) {   // every lane gets the warp's (largest key, its lowest index)
+      const unsigned hi = static_cast<unsigned>(k >> 32), lo = static_cast<unsigned>(k);
+      const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+      const bool c1 = hi == mh;
+      const unsigned ml = __reduce_max_sync(0xffffffffu, c1 ? lo : 0u);
+      const bool c2 = c1 && lo == ml;
+      i = static_cast<int>(__reduce_min_sync(0xffffffffu, c2 ? static_cast<unsigned>(i) : 0x7fffffffu));
+      k = (static_cast<unsigned long long>(mh) << 32) | ml;
+    };
+    unsigned long long my_k = 0ull;
     int my_i = 0x7fffffff;
     auto refresh = [&]() {
-      my_v = -1.0 / 0.0; my_i = 0x7fffffff;
+      my_k = 0ull; my_i = 0x7fffffff;
       for (int c = tid; c < K; c += kSelThreads) {
-        const double v = scores[c];
-        if (v != -1.0 / 0.0 && better(v, c, my_v, my_i)) { my_v = v; my_i = c; }
+        const unsigned long long v = keys[c];
+        if (v > my_k) { my_k = v; my_i = c; }   // ascending c: the lowest index of equal keys stays
       }
     };
     refresh();
     constexpr int nwarps = kSelThreads / 32;
     for (int iter = 0; iter < K; ++iter) {
       if (total_tok >= p.budget) break;
-      double bv = my_v;
+      unsigned long long bk = my_k;
       int bi = my_i;
-      for (int o = 16; o > 0; o >>= 1) {
-        const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-      }
-      if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+      warp_argmax(bk, bi);
+      if (lane == 0) { red_k[warp] = bk; red_i[warp] = bi; }
       sel_sync();
       if (warp == 0) {
-        double v = lane < nwarps ? red_v[lane] : -1.0 / 0.0;
-        int i = lane < nwarps ? red_i[lane] : 0x7fffffff;
-        for (int o = 16; o > 0; o >>= 1) {
-          const double ov = __shfl_xor_sync(0xffffffffu, v, o);
-          const int oi = __shfl_xor_sync(0xffffffffu, i, o);
-          if (better(ov, oi, v, i)) { v = ov; i = oi; }
-        }
+        unsigned long long k2 = lane < nwarps ? red_k[lane] : 0ull;
+        int i2 = lane < nwarps ? red_i[lane] : 0x7fffffff;
+        warp_argmax(k2, i2);
         if (lane == 0) {
-          if (v == -1.0 / 0.0 || i == 0x7fffffff) {
+          if (k2 == 0ull || i2 == 0x7fffffff) {
             total_tok = 0x7fffffff;  // nothing left
             win_s = -1;
           } else {
-            sel_list[n_sel++] = i;
-            total_tok += csize[i];
-            win_s = i;               // the winner, for its owner
+            sel_list[n_sel++] = i2;
+            total_tok += csize[i2];
+            win_s = i2;              // the winner, for its owner
           }
         }
       }
@@ -135,7 +145,7 @@ __device__ __forceinline__ void retrieve_select_body(const RetrieveParams& p, co
       // (win_s is rewritten only behind the next round's first barrier, which no thread passes before it has read it)
       const int won = win_s;
       if (won >= 0 && won % kSelThreads == tid) {
-        scores[won] = -1.0 / 0.0;
+        keys[won] = 0ull;
         refresh();
       }
     }
