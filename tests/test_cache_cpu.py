@@ -21,3 +21,19 @@ def test_split_blocks():
     assert split_blocks(10000, 4096, 1.0) == (10000, 0)
     assert split_blocks(10000, 4096, 0.0) == (0, 10000)
     assert split_blocks(100, 4096, 0.5) == (0, 100) or split_blocks(100, 4096, 0.5) == (100, 0)
+
+
+def test_host_pipeline_chunk_bounds():
+    """HostPrefillPipeline cuts the query rows into a short first chunk, full chunks and a short last chunk; every
+    chunk starts on a multiple of 128 rows, none is longer than chunk_rows, together they cover the sequence once."""
+    import types
+    from longcontext_sqattn_paddle_b200.sqattn import HostPrefillPipeline
+    for n, chunk, edge in ((131072, 8192, 2048), (32768, 8192, 2048), (16384, 8192, 2048), (8192, 8192, 2048),
+                           (5000, 4096, 2048), (20000, 4096, 2048), (128, 4096, 2048), (131000, 8192, 2048), (1664, 512, 128)):
+        cfg = types.SimpleNamespace(chunk=chunk, edge=min(edge, chunk))
+        bounds = HostPrefillPipeline._bounds(cfg, n)
+        assert bounds[0][0] == 0 and bounds[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(bounds, bounds[1:]))
+        assert all(0 < r1 - r0 <= chunk and r0 % 128 == 0 for r0, r1 in bounds)
+        if n > 2 * chunk:
+            assert bounds[0][1] == cfg.edge and bounds[-1][1] - bounds[-1][0] <= cfg.edge + 127
