@@ -424,9 +424,10 @@ class SPHostPrefillPipeline:
     output travels back, so the two copy directions, the collectives and the kernels overlap.  Relative windows."""
 
     def __init__(self, bit8_window_sizes, bit4_window_sizes, sink_window_size, args, seq_total: int, layout="balanced",
-                 chunk_rows: int = 4096, group=None, p_fp8_mode: int = 0, device=None):
-        if chunk_rows % 128:
-            raise ValueError("chunk_rows must be a multiple of 128")
+                 chunk_rows: int = 4096, group=None, p_fp8_mode: int = 0, device=None, edge_rows: int = 1024):
+        if chunk_rows % 128 or edge_rows % 128 or edge_rows <= 0:
+            raise ValueError("chunk_rows and edge_rows must be positive multiples of 128")
+        self.edge = min(int(edge_rows), int(chunk_rows))   # first and last chunk of a row range: their copies overlap with nothing
         if not args.use_relative_distance:
             raise ValueError("the host pipeline is implemented for relative windows")
         self.bit8, self.bit4, self.sink, self.args = bit8_window_sizes, bit4_window_sizes, sink_window_size, args
@@ -464,9 +465,10 @@ class SPHostPrefillPipeline:
                                               world, rank, self.group, self.layout, "halo")
         q_free, o_free = [None, None], [None, None]
         ci, base, waited = 0, 0, False
+        from .sqattn.attn_replacer import chunk_bounds
         for lo, hi in segs:
-            for r0 in range(0, hi - lo, self.chunk):
-                rows, s = min(self.chunk, hi - lo - r0), ci & 1
+            for r0, r1 in chunk_bounds(hi - lo, self.chunk, self.edge):
+                rows, s = r1 - r0, ci & 1
                 with torch.cuda.stream(self.s_in):
                     if q_free[s] is not None:
                         self.s_in.wait_event(q_free[s])

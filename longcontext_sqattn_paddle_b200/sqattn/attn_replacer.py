@@ -86,6 +86,30 @@ def mp_triton_wrapper(layer_idx, bit8_window_sizes=0, bit4_window_sizes=0, sink_
     return attention_fn
 
 
+def chunk_bounds(n: int, chunk: int, edge: int):
+    """Cuts ``n`` query rows into chunks for a copy / compute / copy pipeline: a short first chunk (``edge`` rows: its
+    upload overlaps with nothing), full chunks of ``chunk`` rows, a short last chunk (its download overlaps with
+    nothing).  Every chunk starts on a multiple of 128 rows; sequences of at most two chunks are cut evenly."""
+    cuts = [0]
+    if n > 2 * chunk:
+        cuts.append(edge)
+        r = chunk
+        while r < n - chunk:
+            cuts.append(r)
+            r += chunk
+        cuts.append(r)
+        last = (n - edge) // 128 * 128   # a chunk starts on a multiple of 128 rows
+        if last > r:
+            cuts.append(last)
+    else:
+        r = chunk
+        while r < n:
+            cuts.append(r)
+            r += chunk
+    cuts.append(n)
+    return [(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1) if cuts[i + 1] > cuts[i]]
+
+
 class HostPrefillPipeline:
     """The same operator for callers whose activations live in PINNED HOST memory (layer-wise offloading runtimes
     such as the reference's, which keeps the KV cache on the host during prefill, cache_hub/flash_attn_cache.py):
@@ -113,24 +137,7 @@ class HostPrefillPipeline:
 
     def _bounds(self, n):
         """Row ranges of the chunks: a short first one, full chunks, a short last one."""
-        cuts = [0]
-        if n > 2 * self.chunk:
-            cuts.append(self.edge)
-            r = self.chunk
-            while r < n - self.chunk:
-                cuts.append(r)
-                r += self.chunk
-            cuts.append(r)
-            last = (n - self.edge) // 128 * 128   # a chunk starts on a multiple of 128 rows
-            if last > r:
-                cuts.append(last)
-        else:
-            r = self.chunk
-            while r < n:
-                cuts.append(r)
-                r += self.chunk
-        cuts.append(n)
-        return [(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1) if cuts[i + 1] > cuts[i]]
+        return chunk_bounds(n, self.chunk, self.edge)
 
     def _buffers(self, n, hq, hkv, d, dtype):
         key = (n, hq, hkv, d, dtype)

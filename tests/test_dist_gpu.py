@@ -73,7 +73,7 @@ def _worker(rank, world, port, tmp):
             segs = sqdist._resolve_layout(layout, n, world, reach, sink).segments(rank)
             ref = sqdist.sp_prefill_wrapper(w8, w4, sink, _Args(), seq_total=n, layout=layout)(
                 _Layer(), _rows(q, segs).cuda(), _rows(k, segs).cuda(), _rows(v, segs).cuda(), None)
-            pipe = sqdist.SPHostPrefillPipeline(w8, w4, sink, _Args(), seq_total=n, layout=layout, chunk_rows=256)
+            pipe = sqdist.SPHostPrefillPipeline(w8, w4, sink, _Args(), seq_total=n, layout=layout, chunk_rows=256, edge_rows=128)
             hout = torch.empty(ref.shape, dtype=ref.dtype).pin_memory()
             for _ in range(2):
                 pipe(_rows(q, segs).pin_memory(), _rows(k, segs).pin_memory(), _rows(v, segs).pin_memory(), hout)
