@@ -77,11 +77,12 @@ def test_operator_boundary():
     assert (out.float().cpu() - ref.float()).abs().max().item() < 2e-2
 
 
-def test_host_pipeline_matches_operator():
+@pytest.mark.parametrize("n", [1280 + 384, 1700])
+def test_host_pipeline_matches_operator(n):
     """Pinned host tensors in, pinned host tensor out, chunked over query rows: bit-identical to the one-shot
-    operator (the last chunk is ragged)."""
+    operator (the last chunk is ragged; 1700 tokens: the sequence does not end on a 128-row tile either)."""
     from longcontext_sqattn_paddle_b200.sqattn import HostPrefillPipeline, mp_triton_wrapper
-    hq, hkv, n, d = 8, 2, 1280 + 384, 128
+    hq, hkv, d = 8, 2, 128
     q, k, v = so.make_inputs(13, 1, n, hq, hkv, d, torch.bfloat16)
 
     class Layer:
