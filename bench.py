@@ -270,6 +270,27 @@ class _Layer:
     num_key_value_groups = HQ // HKV
 
 
+def bind_to_gpu_cpus(local_rank: int):
+    """Run this process (and therefore allocate and first-touch its pinned host buffers) on the CPU cores next to
+    its GPU: with several ranks on a two-socket host, pinned buffers on the far socket make every host copy cross
+    the socket link.  Sets only this process's CPU affinity (what `numactl` would do); no GPU setting is touched.
+    Returns the number of cores kept, or None when the topology cannot be read."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 class _Ctx:
     """Rank, device and timing helpers shared by the legs of the GPU arm."""
 
@@ -283,6 +304,7 @@ class _Ctx:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={self.world})")
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
+        self.cpu_cores_bound = bind_to_gpu_cpus(self.local) if self.world > 1 else None
         if self.world > 1:
             dist.init_process_group("nccl", device_id=self.dev)
         self.peaks = load_peaks()
@@ -575,7 +597,8 @@ def run_ours(args):
     ms_e2e = ctx.timed(e2e_step, e2e_steps) / e2e_steps
     e2e = {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": (dq.numel() + dk.numel() + dv.numel()) * 2, "d2h_bytes_per_step": out.numel() * 2,
-           "bytes_are": "per rank", "api": e2e_api, "matches_device_path": e2e_ok, "steps": e2e_steps}
+           "bytes_are": "per rank", "api": e2e_api, "matches_device_path": e2e_ok, "steps": e2e_steps,
+           "cpu_cores_bound_to_gpu": ctx.cpu_cores_bound}
     del hout
 
     # ---- roofline of the dominant kernel: the attention kernel alone on this rank's rows (events on its stream)
