@@ -119,9 +119,10 @@ class HostPrefillPipeline:
     in sequence order: a chunk of rows needs only the V rows up to its own end (causal), so its V rows travel with
     it, are prepared with it and the attention kernel (sqattn_prefill with q_row_offset) starts on the first chunk
     while the rest of V and Q is still on the bus and earlier outputs travel back.  The first and the last chunk are
-    short, because the upload of the first and the download of the last cannot overlap with anything.  H2D copies,
-    kernels and D2H copies run on three streams.  Results are identical to the one-shot operator: chunks only
-    partition the query rows."""
+    short, because the upload of the first and the download of the last cannot overlap with anything.  H2D copies
+    and D2H copies have a stream each, and the chunks' kernels alternate between two streams, so that the attention
+    CTAs of the next chunk fill the SMs the last wave of the previous chunk leaves idle.  Results are identical to the
+    one-shot operator: chunks only partition the query rows."""
 
     def __init__(self, bit8_window_sizes=0, bit4_window_sizes=0, sink_window_size=0, args=None, chunk_rows=4096,
                  p_fp8_mode="off", device=None, edge_rows=2048):
@@ -133,6 +134,7 @@ class HostPrefillPipeline:
         self.fp8 = {"off": L.P_FP8_OFF, "all": L.P_FP8_ALL, "stage2": L.P_FP8_STAGE2}[p_fp8_mode]
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.s_run = [torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)]   # kernels of even / odd chunks
         self._shape, self._buf = None, None
 
     def _bounds(self, n):
@@ -183,10 +185,14 @@ class HostPrefillPipeline:
         cur.wait_event(ev_k)
         ops.prep_qkv(None, buf["k"], None, qk_qtype=a.qk_qtype, v_qtype=a.v_qtype, skip_bit4=True, kv_out_nhd=True,
                      out={"k8": buf["k8"]})
+        for st in self.s_run:
+            st.wait_stream(cur)     # K is prepared, and everything the caller queued before this call is done
         q_free = [None, None]   # compute has finished reading q buffer s
         o_free = [None, None]   # the D2H copy has finished reading output buffer s
+        ev_prep = None          # the previous chunk's V rows are prepared (the next chunk attends them too)
         for ci, (r0, r1) in enumerate(self._bounds(n)):
             rows, s = r1 - r0, ci & 1
+            run = self.s_run[s]     # buffer s is only ever touched by the kernels of stream s
             with torch.cuda.stream(self.s_in):
                 if q_free[s] is not None:
                     self.s_in.wait_event(q_free[s])
@@ -194,18 +200,24 @@ class HostPrefillPipeline:
                 buf["q"][s][:, :rows].copy_(q_host[:, r0:r1], non_blocking=True)
                 ev_q = torch.cuda.Event()
                 ev_q.record(self.s_in)
-            cur.wait_event(ev_q)
-            if o_free[s] is not None:
-                cur.wait_event(o_free[s])
-            q8 = buf["q8"][s][: hq * rows * d].view(1, hq, rows, d)
-            ops.prep_qkv(buf["q"][s][:, :rows], None, buf["v"][:, r0:r1], qk_qtype=a.qk_qtype, v_qtype=a.v_qtype,
-                         skip_bit4=True, kv_out_nhd=True, out={"q8": q8, "v8": buf["v8"][:, r0:r1]})
-            o = buf["o"][s][:, :rows]
-            ops.prefill(q8, buf["k8"], q8, buf["k8"], buf["v8"], mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4,
-                        sink=self.sink, layout="HND", kv_layout="NHD", p_fp8_mode=self.fp8, q_is_scaled=True,
-                        out=o.view(1, rows, hq, d), out_layout="NHD", q_row_offset=r0)
-            ev_c = torch.cuda.Event()
-            ev_c.record(cur)
+            with torch.cuda.stream(run):
+                run.wait_event(ev_q)
+                if o_free[s] is not None:
+                    run.wait_event(o_free[s])
+                q8 = buf["q8"][s][: hq * rows * d].view(1, hq, rows, d)
+                ops.prep_qkv(buf["q"][s][:, :rows], None, buf["v"][:, r0:r1], qk_qtype=a.qk_qtype, v_qtype=a.v_qtype,
+                             skip_bit4=True, kv_out_nhd=True, out={"q8": q8, "v8": buf["v8"][:, r0:r1]})
+                this_prep = torch.cuda.Event()
+                this_prep.record(run)
+                if ev_prep is not None:
+                    run.wait_event(ev_prep)
+                ev_prep = this_prep
+                o = buf["o"][s][:, :rows]
+                ops.prefill(q8, buf["k8"], q8, buf["k8"], buf["v8"], mode=L.MODE_RELATIVE_WINDOW, win8=r8, win4=r4,
+                            sink=self.sink, layout="HND", kv_layout="NHD", p_fp8_mode=self.fp8, q_is_scaled=True,
+                            out=o.view(1, rows, hq, d), out_layout="NHD", q_row_offset=r0)
+                ev_c = torch.cuda.Event()
+                ev_c.record(run)
             q_free[s] = ev_c
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(ev_c)
@@ -213,5 +225,7 @@ class HostPrefillPipeline:
                 ev_o = torch.cuda.Event()
                 ev_o.record(self.s_out)
             o_free[s] = ev_o
+        for st in self.s_run:
+            cur.wait_stream(st)
         cur.wait_stream(self.s_out)
         return out_host
