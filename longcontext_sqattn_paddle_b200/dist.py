@@ -434,6 +434,7 @@ class SPHostPrefillPipeline:
         self.total, self.layout, self.chunk, self.group, self.fp8 = int(seq_total), layout, int(chunk_rows), group, p_fp8_mode
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.s_in, self.s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.s_run = [torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)]   # kernels of even / odd chunks
         self.backend, self.state, self._buf = CudaBackend(), {}, None
 
     def __call__(self, q_host, k_host, v_host, out_host):
@@ -464,29 +465,34 @@ class SPHostPrefillPipeline:
         k8, _, v8, segs, works = _sp_kv_stage(self.state, be, buf["k"], buf["v"], a, win8, win4, self.sink, self.total,
                                               world, rank, self.group, self.layout, "halo")
         q_free, o_free = [None, None], [None, None]
-        ci, base, waited = 0, 0, False
+        ci, base, waited = 0, 0, [False, False]
+        for st in self.s_run:
+            st.wait_stream(cur)       # own K/V rows are prepared; the halo rows are waited for below
         from .sqattn.attn_replacer import chunk_bounds
         for lo, hi in segs:
             for r0, r1 in chunk_bounds(hi - lo, self.chunk, self.edge):
                 rows, s = r1 - r0, ci & 1
+                run = self.s_run[s]   # buffer s is only ever touched by the kernels of stream s; the two streams let
+                                      # the next chunk's CTAs fill the last wave of the previous chunk
                 with torch.cuda.stream(self.s_in):
                     if q_free[s] is not None:
                         self.s_in.wait_event(q_free[s])
                     buf["q"][s][:, :rows].copy_(q_host[:, base + r0:base + r0 + rows], non_blocking=True)
                     ev_q = torch.cuda.Event()
                     ev_q.record(self.s_in)
-                cur.wait_event(ev_q)
-                if o_free[s] is not None:
-                    cur.wait_event(o_free[s])
-                q8, _ = be.prep_q(buf["q"][s][:, :rows], a.qk_qtype, False)
-                if not waited:          # the halo rows have to be in place before the first attention launch
-                    for w in works:
-                        w.wait()
-                    waited = True
-                o = be.windowed_prefill(q8, None, k8, None, v8, win8, win4, self.sink, [(lo + r0, lo + r0 + rows)], True,
-                                        self.fp8, out=buf["o"][s][:, :rows])
-                ev_c = torch.cuda.Event()
-                ev_c.record(cur)
+                with torch.cuda.stream(run):
+                    run.wait_event(ev_q)
+                    if o_free[s] is not None:
+                        run.wait_event(o_free[s])
+                    q8, _ = be.prep_q(buf["q"][s][:, :rows], a.qk_qtype, False)
+                    if not waited[s]:       # the halo rows have to be in place before this stream's first attention launch
+                        for w in works:
+                            w.wait()
+                        waited[s] = True
+                    o = be.windowed_prefill(q8, None, k8, None, v8, win8, win4, self.sink, [(lo + r0, lo + r0 + rows)], True,
+                                            self.fp8, out=buf["o"][s][:, :rows])
+                    ev_c = torch.cuda.Event()
+                    ev_c.record(run)
                 q_free[s] = ev_c
                 with torch.cuda.stream(self.s_out):
                     self.s_out.wait_event(ev_c)
@@ -496,6 +502,8 @@ class SPHostPrefillPipeline:
                 o_free[s] = ev_o
                 ci += 1
             base += hi - lo
+        for st in self.s_run:
+            cur.wait_stream(st)
         cur.wait_stream(self.s_out)
         return out_host
 
