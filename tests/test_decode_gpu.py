@@ -115,13 +115,14 @@ def test_decode_reference_golden(golden_dir, name, fp8):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("fp8", [False, True])
-def test_decode_over_listed_rows_equals_decode_over_packed_copies(dtype, fp8):
+@pytest.mark.parametrize("d", [128, 64])
+def test_decode_over_listed_rows_equals_decode_over_packed_copies(dtype, fp8, d):
     """sqattn_decode_args.gather: attending rows of a cache through an index list gives the bits of attending a
     packed copy of those rows (the kernel's arithmetic is the same, only the producer differs); ragged list lengths,
     one of them empty-tailed inside a 64-key tile, caches with different lengths and a strided row layout."""
     from longcontext_sqattn_paddle_b200 import ops
     g = torch.Generator().manual_seed(21)
-    b, groups, d, cap = 5, 4, 128, 1408
+    b, groups, cap = 5, 4, 1408
     lens_cache = [3000, 777, 5000, 1500, 2048]
     counts = [1408, 300, 1000, 65, 640]
     caches = [(torch.randn(n, 2 * d, generator=g).to(dtype).cuda(), torch.randn(n, 2 * d, generator=g).to(dtype).cuda())
