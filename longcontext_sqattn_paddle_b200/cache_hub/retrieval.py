@@ -49,18 +49,21 @@ class ClusteredKV:
         if self.capacity > self.tokens:
             pad = self.capacity - self.tokens
             self.assign = torch.cat([self.assign, torch.zeros(self.hkv, pad, dtype=torch.int32, device=key.device)], dim=1)
-        # storage: [Hkv, split, D] on the GPU and, for a hybrid layout, [Hkv, capacity - split, D] in pinned host memory
+        # storage: [Hkv, split, 2, D] on the GPU and, for a hybrid layout, [Hkv, capacity - split, 2, D] in pinned host
+        # memory.  A token's key row and value row sit next to each other (rows 2 * D elements apart in both views):
+        # a retrieval step reads scattered tokens, and one 512-byte piece per token costs the DRAM half the page
+        # openings of two 256-byte pieces in two arrays.
         self.split = self.capacity if split < 0 else min(int(split), self.tokens)
         dev_rows = self.split if split >= 0 else self.capacity
-        self.key = torch.empty(self.hkv, dev_rows, self.d, dtype=key.dtype, device=key.device)
-        self.value = torch.empty_like(self.key)
+        self.kv = torch.empty(self.hkv, dev_rows, 2, self.d, dtype=key.dtype, device=key.device)
+        self.key, self.value = self.kv[:, :, 0], self.kv[:, :, 1]
         n_dev = min(self.tokens, dev_rows)
         self.key[:, :n_dev], self.value[:, :n_dev] = key[:, :n_dev], value[:, :n_dev]
         self.key_host = self.value_host = None
         if split >= 0:
             rows = self.capacity - self.split
-            self.key_host = torch.empty(self.hkv, rows, self.d, dtype=key.dtype, pin_memory=True)
-            self.value_host = torch.empty_like(self.key_host).pin_memory()
+            self.kv_host = torch.empty(self.hkv, rows, 2, self.d, dtype=key.dtype, pin_memory=True)
+            self.key_host, self.value_host = self.kv_host[:, :, 0], self.kv_host[:, :, 1]
             self.key_host[:, :self.tokens - self.split].copy_(key[:, self.split:])
             self.value_host[:, :self.tokens - self.split].copy_(value[:, self.split:])
             torch.cuda.synchronize(key.device)
@@ -145,7 +148,7 @@ class ClusteredKV:
         if self.key_host is not None:
             raise ValueError("hybrid layouts gather through RaggedClusteredDecoder.step (the batched entry point)")
         for src, dst in ((self.key, k_out), (self.value, v_out)):
-            L.check(L.lib.sqattn_gather_rows(src.data_ptr(), src.stride(0), self.d, idx.data_ptr(), count.data_ptr(),
+            L.check(L.lib.sqattn_gather_rows(src.data_ptr(), src.stride(0), src.stride(1), idx.data_ptr(), count.data_ptr(),
                                              self.hkv, cap, self.d, dst.data_ptr(), _stream()))
 
 
@@ -190,7 +193,7 @@ class RaggedClusteredDecoder:
             it.tail_start = c.clustered
             it.out_idx, it.out_count = self.idx[i].data_ptr(), self.count[i].data_ptr()
             it.k_src, it.v_src = c.key.data_ptr(), c.value.data_ptr()
-            it.src_group_stride, it.src_row_stride = c.key.stride(0), self.d
+            it.src_group_stride, it.src_row_stride = c.key.stride(0), c.key.stride(1)
             if c.key_host is not None:      # hybrid layout: rows from `split` on are read from pinned host memory
                 it.split_row, it.k_src2, it.v_src2 = c.split, c.key_host.data_ptr(), c.value_host.data_ptr()
                 it.src2_group_stride = c.key_host.stride(0)
@@ -223,7 +226,7 @@ class RaggedClusteredDecoder:
         qv = self._q.view(b * self.hkv, groups, 1, d)
         if self._in_place():
             o = ops.decode_gather(qv, self.idx.view(b * self.hkv, self.cap), self.count.view(-1), self._rows[0], self._rows[1],
-                                  d, q.dtype, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8)
+                                  self.caches[0].key.stride(1), q.dtype, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8)
         else:
             o = ops.decode(qv, self.k_sel, self.v_sel, out_dtype=out_dtype or q.dtype, p_fp8=self.p_fp8, kv_len=self.cap,
                            kv_lens_device=self.count.view(-1))

@@ -3,8 +3,9 @@
 // the KV group, so the group's K/V are read once (the reference reads them once per query head,
 // sqattn/attn_triton_decode.py:204-241).
 //   warp 4      TMA producer: 64-key K and V tiles into a 3-stage shared-memory ring (128-byte swizzle); when the
-//               keys are an index list into a cache, the same warp copies the listed rows into the same layout
-//               with 16-byte asynchronous copies (two rows of K and V per lane and tile)
+//               keys are an index list into a cache, warps 4 and 5 copy the listed rows into the same layout with
+//               16-byte asynchronous copies (D/8 lanes per row, so that a request covers whole 128-byte lines;
+//               each warp takes every other row group).  Warp 5 idles otherwise.
 //   warps 0..3  16 keys of every tile each: S = q K^T and O += P V on mma.sync m16n8k16 (query heads padded
 //               to the 16-row M dimension), warp-shuffle row max / sum, private online-softmax state;
 //               the four states are merged through shared memory at the end of the item.
@@ -103,7 +104,7 @@ __device__ unsigned long long g_dec_first = ~0ull, g_dec_last = 0ull;
 #endif
 
 template <int D, bool BF16>
-__global__ void __launch_bounds__(160, 2)
+__global__ void __launch_bounds__(192, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ DecodeParams p) {
   using L = DecodeSmem<D>;
@@ -154,14 +155,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     *cta_abort = 0;
-    // a stage is full after the producer's one arrival + its bytes (TMA), or after all 32 lanes' copies (index list)
-    for (int i = 0; i < kDecStages; ++i) { mbar_init(bar_full + 8 * i, p.gather_idx ? 32 : 1); mbar_init(bar_empty + 8 * i, 4); }
+    // a stage is full after the producer's one arrival + its bytes (TMA), or after the copies of all 64 lanes of the
+    // two copying warps (index list)
+    for (int i = 0; i < kDecStages; ++i) { mbar_init(bar_full + 8 * i, p.gather_idx ? 64 : 1); mbar_init(bar_empty + 8 * i, 4); }
     fence_barrier_init();
     fence_proxy_async();
   }
   __syncthreads();
 
-  if (warp == 4 && p.gather_idx) {
+  if (warp >= 4 && p.gather_idx) {
+    const int half = warp - 4;   // warps 4 and 5 copy the even and the odd row groups of every tile
     const long long grp = static_cast<long long>(bi) * p.hkv + kvh;
     const int* idx = p.gather_idx + grp * p.gather_cap;
     const uint8_t* kb = p.gather_k[grp];
@@ -183,24 +186,27 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * st, ((t / kDecStages) & 1) ^ 1, cta_abort, 201));
       if (!ok) break;
       const uint32_t k_tile = sbase + st * L::kStageBytes, v_tile = k_tile + L::kTileBytes;
-#pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = lane + 32 * rr;
-        if (tok[rr] >= 0) {
-          const long long off = static_cast<long long>(tok[rr]) * p.gather_row_stride * 2;
-#pragma unroll
-          for (int c = 0; c < D / 8; ++c) {
-            cp_async_16(k_tile + tile_off(r, c), kb + off + c * 16);
-            cp_async_16(v_tile + tile_off(r, c), vb + off + c * 16);
-          }
+      // D / 8 consecutive lanes copy one row (whole 128-byte lines per request); lane l holds the list entries of
+      // rows l and l + 32 of the tile and hands them out by shuffle
+      constexpr int kLanesPerRow = D / 8, kRowsPerInstr = 32 / kLanesPerRow;
+      const int c = lane % kLanesPerRow, rsel = lane / kLanesPerRow;
+#pragma unroll 4
+      for (int r0 = half * kRowsPerInstr; r0 < kDecTile; r0 += 2 * kRowsPerInstr) {
+        const int r = r0 + rsel;
+        const int t_lo = __shfl_sync(0xffffffffu, tok[0], r & 31), t_hi = __shfl_sync(0xffffffffu, tok[1], r & 31);
+        const int tk = r < 32 ? t_lo : t_hi;
+        if (tk >= 0) {
+          const long long off = static_cast<long long>(tk) * p.gather_row_stride * 2 + c * 16;
+          cp_async_16(k_tile + tile_off(r, c), kb + off);
+          cp_async_16(v_tile + tile_off(r, c), vb + off);
         }
       }
       cp_async_arrive(bar_full + 8 * st);
       tok[0] = nxt[0]; tok[1] = nxt[1];
     }
     asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp is in flight when the CTA winds down
-  } else if (warp == 4) {
-    if (lane == 0) {
+  } else if (warp >= 4) {
+    if (warp == 4 && lane == 0) {
       tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
       bool ok = true;
       for (int t = 0; ok && t < ntiles; ++t) {

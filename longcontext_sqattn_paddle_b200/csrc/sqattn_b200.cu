@@ -378,7 +378,7 @@ int launch_decode(const sqattn_decode_args* a, const DecodePlan& pl, cudaStream_
   }
   if (pl.total_items > 0) {
     dim3 grid(pl.total_items, a->num_kv_heads);
-    SQ_CUDA(launch_overlapped(2, decode_kernel<D, BF16>, grid, dim3(160), L::kDynBytes, stream, tk, tv, p));
+    SQ_CUDA(launch_overlapped(2, decode_kernel<D, BF16>, grid, dim3(192), L::kDynBytes, stream, tk, tv, p));
   }
 
   if (a->peer) {
